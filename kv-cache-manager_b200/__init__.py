@@ -12,7 +12,7 @@ kernels, a true float32 path and trace replay.
     print(eng.take_finished()[0].generated())
 """
 from . import config, models, parts, weights
-from .config import (ConfigError, EngineConfig, KVManagerConfig, LlamaConfig, SchedulerConfig,
+from .config import (ConfigError, EngineConfig, KVManagerConfig, LlamaConfig, SchedulerConfig, TolanexConfig,
                      load_config, register_architecture, registered_architectures)
 from .weights import WeightError, write_random_model
 
@@ -27,6 +27,6 @@ def __getattr__(name):
 
 
 __all__ = ["config", "models", "parts", "weights", "ConfigError", "EngineConfig",
-           "KVManagerConfig", "LlamaConfig", "SchedulerConfig", "load_config",
+           "KVManagerConfig", "LlamaConfig", "SchedulerConfig", "TolanexConfig", "load_config",
            "register_architecture", "registered_architectures", "WeightError",
            "write_random_model", "Engine", "ModelRunner", "load_model", "generate"]

@@ -81,7 +81,7 @@ class CachePools:
         for g in plan.groups:
             shape = (len(g.sites), num_blocks, g.spec.num_kv_heads, block_size, g.spec.head_dim)
             self.k.append(torch.zeros(shape, dtype=dtype, device=device))
-            self.v.append(torch.zeros(shape, dtype=dtype, device=device))
+            self.v.append(torch.zeros(shape, dtype=dtype, device=device) if g.spec.values else None)
         self.state: List[Optional[torch.Tensor]] = [
             None if s is None else torch.zeros((num_slots, *s.shape), dtype=s.dtype, device=device)
             for s in plan.site_state]
@@ -90,7 +90,7 @@ class CachePools:
             g = plan.site_group[k]
             self.sites.append(SiteCache(
                 group=g, k=self.k[g][plan.site_layer[k]] if g >= 0 else None,
-                v=self.v[g][plan.site_layer[k]] if g >= 0 else None,
+                v=self.v[g][plan.site_layer[k]] if g >= 0 and self.v[g] is not None else None,
                 writes=plan.site_writes[k], state=self.state[k]))
 
     def reset_slot(self, slot: int) -> None:
@@ -100,11 +100,11 @@ class CachePools:
                 s[slot].zero_()
 
     def total_bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self.k + self.v)
+        return sum(t.numel() * t.element_size() for t in self.k + self.v if t is not None)
 
 
 def bytes_per_block(plan: CachePlan, block_size: int, dtype: torch.dtype) -> int:
     """K and V of one page id across every site of every group (``src/cuda/kv_cache.h:20-23``)."""
     item = torch.empty((), dtype=dtype).element_size()
-    return sum(2 * len(g.sites) * g.spec.num_kv_heads * block_size * g.spec.head_dim * item
+    return sum((2 if g.spec.values else 1) * len(g.sites) * g.spec.num_kv_heads * block_size * g.spec.head_dim * item
                for g in plan.groups)

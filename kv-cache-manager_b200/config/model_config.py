@@ -163,3 +163,125 @@ def read_config_json(folder: str) -> Dict[str, Any]:
     if not isinstance(d, dict):
         raise ConfigError(f"{path}: top level must be a JSON object")
     return d
+
+
+# ------------------------------------------------------------------------------------ Tolanex
+
+def _section(d: Dict[str, Any], key: str, where: str, optional: bool = False) -> Optional[Dict[str, Any]]:
+    v = d.get(key)
+    if v is None:
+        if optional:
+            return None
+        raise ConfigError(f"{where}: required section '{key}' is missing")
+    if not isinstance(v, dict):
+        raise ConfigError(f"{where}: '{key}' must be an object, got {v!r}")
+    return v
+
+
+@dataclass(frozen=True)
+class TolanexConfig(ModelConfig):
+    """Tolanex: a decoder whose layers are listed one by one in config.json.
+
+    Top level: ``vocab``, ``width``, ``max_positions`` (rows of the learned position table),
+    ``norm.eps``, ``residual_mult``, ``embedding.bigram`` {buckets, mul_prev, mul_cur} (optional) and
+    ``layers``: a list of {type, mixer, mlp}.  ``type`` "delta": mixer {heads, kv_heads, dim, vdim,
+    conv}; "latent_attention": mixer {heads, dim, vdim, kv_rank, scale, kv_from (optional: the layer
+    whose cached latent this one reads)}.  ``mlp`` is null or {kind: "moe", expert.ff, router
+    {experts, top, scale, groups {count, keep}}, shared {ff} (optional)}.  ``layers`` is kept as the
+    parsed JSON (a tuple of dicts) after validation; the builder reads every size from it."""
+    vocab: int = 0
+    width: int = 0
+    max_positions: int = 0
+    norm_eps: float = 1e-6
+    residual_mult: float = 1.0
+    bigram_buckets: int = 0
+    bigram_mul_prev: int = 0
+    bigram_mul_cur: int = 0
+    layers: tuple = ()
+
+    @classmethod
+    def from_json_dict(cls, d: Dict[str, Any]) -> "TolanexConfig":
+        w = "config.json (Tolanex)"
+        norm = _section(d, "norm", w)
+        emb = _section(d, "embedding", w, optional=True) or {}
+        big = _section(emb, "bigram", w + " embedding", optional=True)
+        layers = d.get("layers")
+        if not isinstance(layers, list) or not layers:
+            raise ConfigError(f"{w}: 'layers' must be a non-empty list")
+        cfg = cls(
+            architecture="Tolanex",
+            vocab=_require(d, "vocab", int, w),
+            width=_require(d, "width", int, w),
+            max_positions=int(d.get("max_positions") or 0),
+            norm_eps=_require(norm, "eps", float, w + " norm"),
+            residual_mult=float(d.get("residual_mult", 1.0)),
+            bigram_buckets=_require(big, "buckets", int, w + " bigram") if big else 0,
+            bigram_mul_prev=_require(big, "mul_prev", int, w + " bigram") if big else 0,
+            bigram_mul_cur=_require(big, "mul_cur", int, w + " bigram") if big else 0,
+            layers=tuple(json.loads(json.dumps(layers))),
+        )
+        cfg.validate()
+        return cfg
+
+    def validate(self) -> None:
+        w = "TolanexConfig"
+        for f in ("vocab", "width"):
+            if getattr(self, f) <= 0:
+                raise ConfigError(f"{w}: '{f}' must be positive, got {getattr(self, f)}")
+        if self.max_positions < 0 or self.bigram_buckets < 0:
+            raise ConfigError(f"{w}: 'max_positions' and 'bigram.buckets' cannot be negative")
+        if not (self.norm_eps > 0):
+            raise ConfigError(f"{w}: norm.eps must be positive, got {self.norm_eps}")
+        for i, layer in enumerate(self.layers):
+            lw = f"{w}: layer {i}"
+            if not isinstance(layer, dict):
+                raise ConfigError(f"{lw} must be an object")
+            kind = layer.get("type")
+            m = _section(layer, "mixer", lw)
+            if kind == "delta":
+                for k in ("heads", "kv_heads", "dim", "vdim", "conv"):
+                    if _require(m, k, int, lw + " mixer") <= 0:
+                        raise ConfigError(f"{lw}: mixer.{k} must be positive")
+                if m["heads"] % m["kv_heads"]:
+                    raise ConfigError(f"{lw}: mixer.heads ({m['heads']}) must be a multiple of mixer.kv_heads ({m['kv_heads']})")
+            elif kind == "latent_attention":
+                for k in ("heads", "dim", "vdim", "kv_rank"):
+                    if _require(m, k, int, lw + " mixer") <= 0:
+                        raise ConfigError(f"{lw}: mixer.{k} must be positive")
+                _require(m, "scale", float, lw + " mixer")
+                src = m.get("kv_from")
+                if src is not None:
+                    ok = isinstance(src, int) and 0 <= src < i and self.layers[src].get("type") == "latent_attention" \
+                        and self.layers[src]["mixer"].get("kv_from") is None \
+                        and self.layers[src]["mixer"].get("kv_rank") == m["kv_rank"]
+                    if not ok:
+                        raise ConfigError(f"{lw}: mixer.kv_from = {src!r} must name an earlier latent_attention layer "
+                                          f"with a latent of its own and the same kv_rank")
+            else:
+                raise ConfigError(f"{lw}: unknown type {kind!r} (known: delta, latent_attention)")
+            mlp = layer.get("mlp")
+            if mlp is None:
+                continue
+            if not isinstance(mlp, dict) or mlp.get("kind") != "moe":
+                raise ConfigError(f"{lw}: mlp must be null or of kind 'moe', got {mlp!r}")
+            if _require(_section(mlp, "expert", lw + " mlp"), "ff", int, lw + " mlp.expert") <= 0:
+                raise ConfigError(f"{lw}: mlp.expert.ff must be positive")
+            r = _section(mlp, "router", lw + " mlp")
+            experts, top = _require(r, "experts", int, lw + " router"), _require(r, "top", int, lw + " router")
+            groups = _section(r, "groups", lw + " router", optional=True) or {"count": 1, "keep": 1}
+            count, keep = _require(groups, "count", int, lw + " groups"), _require(groups, "keep", int, lw + " groups")
+            if experts <= 0 or count <= 0 or experts % count or not (1 <= keep <= count) \
+                    or not (1 <= top <= experts // count * keep):
+                raise ConfigError(f"{lw}: router cannot choose {top} of {experts} experts in {count} groups of which {keep} are kept")
+            shared = _section(mlp, "shared", lw + " mlp", optional=True)
+            if shared is not None and _require(shared, "ff", int, lw + " mlp.shared") <= 0:
+                raise ConfigError(f"{lw}: mlp.shared.ff must be positive")
+
+    def to_json_dict(self) -> Dict[str, Any]:
+        d: Dict[str, Any] = {"architecture": self.architecture, "vocab": self.vocab, "width": self.width,
+                             "max_positions": self.max_positions, "norm": {"eps": self.norm_eps},
+                             "residual_mult": self.residual_mult, "layers": json.loads(json.dumps(list(self.layers)))}
+        if self.bigram_buckets:
+            d["embedding"] = {"bigram": {"buckets": self.bigram_buckets, "mul_prev": self.bigram_mul_prev,
+                                         "mul_cur": self.bigram_mul_cur}}
+        return d

@@ -42,8 +42,11 @@ def get_architecture(name: str) -> ArchitectureEntry:
 
 def config_from_dict(d: Dict[str, Any]) -> ModelConfig:
     archs = d.get("architectures")
+    if archs is None and isinstance(d.get("architecture"), str):      # the singular form names one architecture
+        archs = [d["architecture"]]
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json: key 'architectures' must be a non-empty list of names")
+        raise ConfigError("config.json: key 'architectures' must be a non-empty list of names "
+                          "(or 'architecture' one name)")
     return get_architecture(archs[0]).config_cls.from_json_dict(d)
 
 

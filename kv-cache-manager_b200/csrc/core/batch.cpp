@@ -20,7 +20,7 @@ BatchBuilder::BatchBuilder(int block_size, int max_blocks_per_seq, int num_group
 
 int64_t BatchBuilder::capacity_for(int rows, int seqs, int logit_rows) const {
   const int64_t tiles = rows / tile_rows_ + seqs + 1;
-  return round4(rows) * (3 + groups_) + round4(seqs) * 4 + round4(logit_rows) + round4(tiles) * 2 +
+  return round4(rows) * (4 + groups_) + round4(seqs) * 4 + round4(logit_rows) + round4(tiles) * 2 +
          round4(int64_t(groups_) * seqs * max_blocks_) + 64;
 }
 
@@ -86,12 +86,14 @@ BatchLayout BatchBuilder::build(const std::vector<BatchEntry>& entries, int32_t*
   L.off_tile_seq = take(tiles);
   L.off_tile_q0 = take(tiles);
   L.off_block_tables = take(int64_t(groups_) * L.seqs * max_blocks_);
+  L.off_prev_tokens = take(L.rows);
   L.total_ints = at;
   if (at > capacity)
     throw std::runtime_error("batch: step needs " + std::to_string(at) + " ints, buffer holds " +
                              std::to_string(capacity));
   std::fill(out, out + at, 0);
   std::fill(out + L.off_slot_mapping, out + L.off_slot_mapping + int64_t(groups_) * L.rows, -1);
+  std::fill(out + L.off_prev_tokens, out + L.off_prev_tokens + L.rows, -1);
   std::fill(out + L.off_seq_state_slot, out + L.off_seq_state_slot + L.seqs, -1);
   std::fill(out + L.off_block_tables, out + L.off_block_tables + int64_t(groups_) * L.seqs * max_blocks_, -1);
 
@@ -128,6 +130,7 @@ BatchLayout BatchBuilder::build(const std::vector<BatchEntry>& entries, int32_t*
     for (int j = 0; j < en.num_tokens; ++j) {
       out[L.off_tokens + row + j] = s.tokens[en.start + j];
       out[L.off_positions + row + j] = en.start + j;
+      out[L.off_prev_tokens + row + j] = en.start + j > 0 ? s.tokens[en.start + j - 1] : -1;
       out[L.off_row_seq + row + j] = si;
     }
     if (en.num_tokens > 1)

@@ -5,6 +5,7 @@
 // Rows are laid out with single-token entries (decodes) first and longer portions after them,
 // so that the two attention kernels each take one contiguous range of rows.  Arrays:
 //   tokens[T] positions[T] row_seq[T]          per row
+//   prev_tokens[T]                              per row: the request's token one position earlier, -1 at position 0
 //   slot_mapping[G][T]                          per group and row: page*B + offset, -1 = skip
 //   seq_q_start[S] seq_q_len[S] seq_ctx_len[S] seq_state_slot[S]   per entry (ctx = start + n)
 //   logit_rows[L]                               rows whose logits are wanted, in the caller's order
@@ -39,6 +40,7 @@ struct BatchLayout {
   int64_t off_tokens = 0, off_positions = 0, off_row_seq = 0, off_slot_mapping = 0;
   int64_t off_seq_q_start = 0, off_seq_q_len = 0, off_seq_ctx_len = 0, off_seq_state_slot = 0;
   int64_t off_logit_rows = 0, off_tile_seq = 0, off_tile_q0 = 0, off_block_tables = 0;
+  int64_t off_prev_tokens = 0;
   int64_t total_ints = 0;
   std::vector<int32_t> entry_order;       // sorted position -> index in the caller's list
 };

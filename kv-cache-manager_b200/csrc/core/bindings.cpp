@@ -285,6 +285,7 @@ PYBIND11_MODULE(kvcm_core, m) {
       .def_readonly("off_tile_seq", &BatchLayout::off_tile_seq)
       .def_readonly("off_tile_q0", &BatchLayout::off_tile_q0)
       .def_readonly("off_block_tables", &BatchLayout::off_block_tables)
+      .def_readonly("off_prev_tokens", &BatchLayout::off_prev_tokens)
       .def_readonly("total_ints", &BatchLayout::total_ints)
       .def_readonly("entry_order", &BatchLayout::entry_order);
 

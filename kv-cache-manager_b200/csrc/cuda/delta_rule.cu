@@ -1,0 +1,281 @@
+// The gated delta rule as a mixer with fixed-size state per request.
+//
+// Per value head (its query/key head is head / (heads / qk_heads)), with S a float matrix
+// [dk, dv] that starts at zero and is carried from token to token:
+//     S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+// q, k, v come from projections that pass a short causal convolution over time per channel and
+// SiLU; q and k are then scaled to unit length per head (q also by dk^-1/2); beta = sigmoid(b),
+// g = exp(-exp(A_log) softplus(a + dt_bias)).  The head's output is divided by its root mean
+// square, multiplied by a weight over dv and by SiLU of a gate projection.
+//
+// State of a request (one float slab per call site, `state_stride` floats a slot):
+//     [ S: heads x dk x dv | last taps-1 inputs of the convolution: (taps-1) x channels ]
+// Everything after the projections is float here, in both storage types.
+//
+// The columns of S are independent of each other, so the recurrence is spread over
+// (request, head, 32 columns) blocks; inside a block four lanes share a column (rows r, r+4, ...
+// each) and add their partial dot products by shuffles.  The same kernel serves portions of
+// prompts and single decoded tokens: it walks the request's rows of the step in order.
+#include "common.cuh"
+
+namespace kvcm {
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+
+// ------------------------------------------------------------------ convolution over time + SiLU
+// out[row, c] = silu( sum_j w[c, j] * in(local - (taps-1-j)) ), in(l) = this step's row l of the
+// request when l >= 0, else what the state kept of earlier steps (zeros at the very start).
+template <typename T>
+__global__ void __launch_bounds__(256)
+delta_conv_kernel(const T* __restrict__ proj, int ldp, const float* __restrict__ conv_w, int taps,
+                  const float* __restrict__ state, long long state_stride, long long conv_off,
+                  const int* __restrict__ row_seq, const int* __restrict__ seq_q_start,
+                  const int* __restrict__ seq_state_slot, float* __restrict__ out, int channels) {
+  const int row = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  const int s = row_seq[row];
+  const int q0 = seq_q_start[s];
+  const int slot = seq_state_slot[s];
+  const int local = row - q0;
+  const float* kept = slot >= 0 ? state + slot * state_stride + conv_off : nullptr;
+  float acc = 0.f;
+  for (int j = 0; j < taps; ++j) {
+    const int l = local - (taps - 1 - j);
+    float v;
+    if (l >= 0) v = ldf(proj + size_t(q0 + l) * ldp + c);
+    else v = kept ? kept[size_t(taps - 1 + l) * channels + c] : 0.f;
+    acc = fmaf(conv_w[size_t(c) * taps + j], v, acc);
+  }
+  out[size_t(row) * channels + c] = silu_f(acc);
+}
+
+// After the convolution has read it: the state keeps the last taps-1 inputs of each request.
+// One thread owns one (request, channel) and moves old entries down before it overwrites them.
+template <typename T>
+__global__ void __launch_bounds__(256)
+delta_conv_state_kernel(const T* __restrict__ proj, int ldp, int taps, float* __restrict__ state,
+                        long long state_stride, long long conv_off, const int* __restrict__ seq_q_start,
+                        const int* __restrict__ seq_q_len, const int* __restrict__ seq_state_slot, int channels) {
+  const int s = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int slot = seq_state_slot[s];
+  if (c >= channels || slot < 0) return;
+  const int q0 = seq_q_start[s], n = seq_q_len[s];
+  float* kept = state + slot * state_stride + conv_off;
+  for (int j = 0; j < taps - 1; ++j) {
+    const int l = n - (taps - 1) + j;
+    const float v = l >= 0 ? ldf(proj + size_t(q0 + l) * ldp + c) : kept[size_t(n + j) * channels + c];
+    kept[size_t(j) * channels + c] = v;
+  }
+}
+
+// ------------------------------------------------------------ unit vectors, step sizes, decays
+// qkv[row]: the first 2 * qk_heads heads of dk (queries, then keys) become unit vectors
+// (x / sqrt(sum x^2 + 1e-6); queries also times dk^-1/2).  ba[row] = [b | a] becomes [beta | g].
+__global__ void __launch_bounds__(128)
+delta_prepare_kernel(float* __restrict__ qkv, int channels, float* __restrict__ ba, const float* __restrict__ a_log,
+                     const float* __restrict__ dt_bias, int heads, int qk_heads, int dk) {
+  const int row = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const float qscale = 1.f / sqrtf(float(dk));
+  for (int hh = warp; hh < 2 * qk_heads; hh += nwarps) {
+    float* p = qkv + size_t(row) * channels + size_t(hh) * dk;
+    float ss = 0.f;
+    for (int i = lane; i < dk; i += 32) ss += p[i] * p[i];
+    ss = warp_sum(ss);
+    float inv = 1.f / sqrtf(ss + 1e-6f);
+    if (hh < qk_heads) inv *= qscale;
+    for (int i = lane; i < dk; i += 32) p[i] *= inv;
+  }
+  for (int h = threadIdx.x; h < heads; h += blockDim.x) {
+    float* r = ba + size_t(row) * 2 * heads;
+    const float b = r[h];
+    const float a = r[heads + h] + dt_bias[h];
+    const float sp = a > 20.f ? a : log1pf(expf(a));
+    r[h] = 1.f / (1.f + expf(-b));
+    r[heads + h] = expf(-expf(a_log[h]) * sp);
+  }
+}
+
+// ------------------------------------------------------------------------------ the recurrence
+constexpr int DR_TOKENS = 16;    // tokens staged in shared memory at a time
+constexpr int DR_COLS = 32;      // columns of S per block
+constexpr int DR_LANES = 4;      // lanes that share a column
+
+template <int NI>                // rows of S per thread: dk <= 4 * NI
+__global__ void __launch_bounds__(DR_COLS * DR_LANES)
+delta_scan_kernel(const float* __restrict__ qkv, int channels, const float* __restrict__ bg,
+                  float* __restrict__ state, long long state_stride, const int* __restrict__ seq_q_start,
+                  const int* __restrict__ seq_q_len, const int* __restrict__ seq_state_slot,
+                  float* __restrict__ out, int heads, int qk_heads, int dk, int dv) {
+  constexpr int DKP = DR_LANES * NI;
+  __shared__ float qs[DR_TOKENS][DKP];
+  __shared__ float ks[DR_TOKENS][DKP];
+  __shared__ float vs[DR_TOKENS][DR_COLS];
+  __shared__ float bs[DR_TOKENS], gs[DR_TOKENS];
+  const int s = blockIdx.z, head = blockIdx.y;
+  const int slot = seq_state_slot[s];
+  if (slot < 0) return;
+  const int q0 = seq_q_start[s], n = seq_q_len[s];
+  const int qk_head = head / (heads / qk_heads);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col_local = warp * 8 + (lane & 7);
+  const int col = blockIdx.x * DR_COLS + col_local;
+  const int r = lane >> 3;
+  const bool col_ok = col < dv;
+  float* S = state + slot * state_stride + (size_t(head) * dk) * dv + col;
+  float acc[NI];
+#pragma unroll
+  for (int m = 0; m < NI; ++m) {
+    const int i = r + DR_LANES * m;
+    acc[m] = (col_ok && i < dk) ? S[size_t(i) * dv] : 0.f;
+  }
+  const size_t q_off = size_t(qk_head) * dk, k_off = size_t(qk_heads + qk_head) * dk;
+  const size_t v_off = size_t(2 * qk_heads) * dk + size_t(head) * dv + size_t(blockIdx.x) * DR_COLS;
+  for (int t0 = 0; t0 < n; t0 += DR_TOKENS) {
+    const int nt = min(DR_TOKENS, n - t0);
+    __syncthreads();                                   // the previous tile has been consumed
+    for (int idx = threadIdx.x; idx < DR_TOKENS * DKP; idx += blockDim.x) {
+      const int t = idx / DKP, i = idx % DKP;
+      const bool ok = t < nt && i < dk;
+      const float* src = qkv + size_t(q0 + t0 + t) * channels;
+      qs[t][i] = ok ? src[q_off + i] : 0.f;
+      ks[t][i] = ok ? src[k_off + i] : 0.f;
+    }
+    for (int idx = threadIdx.x; idx < DR_TOKENS * DR_COLS; idx += blockDim.x) {
+      const int t = idx / DR_COLS, c = idx % DR_COLS;
+      const bool ok = t < nt && blockIdx.x * DR_COLS + c < dv;
+      vs[t][c] = ok ? qkv[size_t(q0 + t0 + t) * channels + v_off + c] : 0.f;
+    }
+    if (threadIdx.x < DR_TOKENS) {
+      const int t = threadIdx.x;
+      bs[t] = t < nt ? bg[size_t(q0 + t0 + t) * 2 * heads + head] : 0.f;
+      gs[t] = t < nt ? bg[size_t(q0 + t0 + t) * 2 * heads + heads + head] : 1.f;
+    }
+    __syncthreads();
+    for (int t = 0; t < nt; ++t) {
+      const float g = gs[t], beta = bs[t];
+      float p = 0.f;
+#pragma unroll
+      for (int m = 0; m < NI; ++m) p = fmaf(acc[m], ks[t][r + DR_LANES * m], p);
+      p += __shfl_xor_sync(0xffffffffu, p, 8);
+      p += __shfl_xor_sync(0xffffffffu, p, 16);
+      const float u = beta * (vs[t][col_local] - g * p);
+      float o = 0.f;
+#pragma unroll
+      for (int m = 0; m < NI; ++m) {
+        acc[m] = fmaf(ks[t][r + DR_LANES * m], u, g * acc[m]);
+        o = fmaf(acc[m], qs[t][r + DR_LANES * m], o);
+      }
+      o += __shfl_xor_sync(0xffffffffu, o, 8);
+      o += __shfl_xor_sync(0xffffffffu, o, 16);
+      if (r == 0 && col_ok) out[size_t(q0 + t0 + t) * heads * dv + size_t(head) * dv + col] = o;
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < NI; ++m) {
+    const int i = r + DR_LANES * m;
+    if (col_ok && i < dk) S[size_t(i) * dv] = acc[m];
+  }
+}
+
+// --------------------------------------------------------------- gated norm of the heads' outputs
+// out[row, h, j] = storage( o[row, h, j] / sqrt(mean_j o^2 + eps) * w[j] * silu(gate[row, h, j]) )
+template <typename T>
+__global__ void __launch_bounds__(128)
+gated_rms_kernel(const float* __restrict__ o, const T* __restrict__ gate, int ldg, const float* __restrict__ w,
+                 T* __restrict__ out, int heads, int dv, float eps) {
+  const int row = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int h = warp; h < heads; h += nwarps) {
+    const float* p = o + size_t(row) * heads * dv + size_t(h) * dv;
+    float ss = 0.f;
+    for (int j = lane; j < dv; j += 32) ss += p[j] * p[j];
+    ss = warp_sum(ss);
+    const float inv = 1.f / sqrtf(ss / float(dv) + eps);
+    for (int j = lane; j < dv; j += 32) {
+      const float gz = ldf(gate + size_t(row) * ldg + size_t(h) * dv + j);
+      stf(out + size_t(row) * heads * dv + size_t(h) * dv + j, p[j] * inv * w[j] * silu_f(gz));
+    }
+  }
+}
+
+template <typename T>
+int launch_delta_conv(const void* proj, int ldp, const float* conv_w, int taps, float* state, long long state_stride,
+                      long long conv_off, const int* row_seq, const int* seq_q_start, const int* seq_q_len,
+                      const int* seq_state_slot, float* out, int rows, int seqs, int channels, cudaStream_t s) {
+  if (rows == 0) return 0;
+  if (taps < 1) return KVCM_ERR_UNSUPPORTED;
+  const int by = (channels + 255) / 256;
+  delta_conv_kernel<T><<<dim3(rows, by), 256, 0, s>>>((const T*)proj, ldp, conv_w, taps, state, state_stride, conv_off,
+                                                      row_seq, seq_q_start, seq_state_slot, out, channels);
+  int rc = KVCM_LAUNCH_RESULT();
+  if (rc || taps == 1) return rc;
+  delta_conv_state_kernel<T><<<dim3(seqs, by), 256, 0, s>>>((const T*)proj, ldp, taps, state, state_stride, conv_off,
+                                                            seq_q_start, seq_q_len, seq_state_slot, channels);
+  return KVCM_LAUNCH_RESULT();
+}
+
+}  // namespace kvcm
+
+using namespace kvcm;
+
+KVCM_API int kvcm_delta_conv_f32(const void* proj, int ldp, const float* conv_w, int taps, float* state,
+                                 long long state_stride, long long conv_off, const int* row_seq,
+                                 const int* seq_q_start, const int* seq_q_len, const int* seq_state_slot, float* out,
+                                 int rows, int seqs, int channels, void* stream) {
+  return launch_delta_conv<float>(proj, ldp, conv_w, taps, state, state_stride, conv_off, row_seq, seq_q_start,
+                                  seq_q_len, seq_state_slot, out, rows, seqs, channels, (cudaStream_t)stream);
+}
+KVCM_API int kvcm_delta_conv_bf16(const void* proj, int ldp, const float* conv_w, int taps, float* state,
+                                  long long state_stride, long long conv_off, const int* row_seq,
+                                  const int* seq_q_start, const int* seq_q_len, const int* seq_state_slot, float* out,
+                                  int rows, int seqs, int channels, void* stream) {
+  return launch_delta_conv<bf16>(proj, ldp, conv_w, taps, state, state_stride, conv_off, row_seq, seq_q_start,
+                                 seq_q_len, seq_state_slot, out, rows, seqs, channels, (cudaStream_t)stream);
+}
+
+KVCM_API int kvcm_delta_prepare(float* qkv, int channels, float* ba, const float* a_log, const float* dt_bias,
+                                int rows, int heads, int qk_heads, int dk, void* stream) {
+  if (rows == 0) return 0;
+  delta_prepare_kernel<<<rows, 128, 0, (cudaStream_t)stream>>>(qkv, channels, ba, a_log, dt_bias, heads, qk_heads, dk);
+  return KVCM_LAUNCH_RESULT();
+}
+
+// Largest key size the recurrence kernel holds in registers.
+KVCM_API int kvcm_delta_scan_max_dk() { return DR_LANES * 64; }
+
+KVCM_API int kvcm_delta_scan(const float* qkv, int channels, const float* bg, float* state, long long state_stride,
+                             const int* seq_q_start, const int* seq_q_len, const int* seq_state_slot, float* out,
+                             int seqs, int heads, int qk_heads, int dk, int dv, void* stream) {
+  if (seqs == 0) return 0;
+  if (dk < 1 || dk > DR_LANES * 64 || qk_heads < 1 || heads % qk_heads) return KVCM_ERR_UNSUPPORTED;
+  const dim3 grid((dv + DR_COLS - 1) / DR_COLS, heads, seqs), block(DR_COLS * DR_LANES);
+  cudaStream_t s = (cudaStream_t)stream;
+#define KVCM_SCAN(NI)                                                                                              \
+  delta_scan_kernel<NI><<<grid, block, 0, s>>>(qkv, channels, bg, state, state_stride, seq_q_start, seq_q_len,     \
+                                               seq_state_slot, out, heads, qk_heads, dk, dv)
+  const int need = (dk + DR_LANES - 1) / DR_LANES;
+  if (need <= 2) KVCM_SCAN(2);
+  else if (need <= 4) KVCM_SCAN(4);
+  else if (need <= 8) KVCM_SCAN(8);
+  else if (need <= 16) KVCM_SCAN(16);
+  else if (need <= 32) KVCM_SCAN(32);
+  else KVCM_SCAN(64);
+#undef KVCM_SCAN
+  return KVCM_LAUNCH_RESULT();
+}
+
+KVCM_API int kvcm_gated_rms_f32(const float* o, const void* gate, int ldg, const float* w, void* out, int rows,
+                                int heads, int dv, float eps, void* stream) {
+  if (rows == 0) return 0;
+  gated_rms_kernel<float><<<rows, 128, 0, (cudaStream_t)stream>>>(o, (const float*)gate, ldg, w, (float*)out, heads, dv, eps);
+  return KVCM_LAUNCH_RESULT();
+}
+KVCM_API int kvcm_gated_rms_bf16(const float* o, const void* gate, int ldg, const float* w, void* out, int rows,
+                                 int heads, int dv, float eps, void* stream) {
+  if (rows == 0) return 0;
+  gated_rms_kernel<bf16><<<rows, 128, 0, (cudaStream_t)stream>>>(o, (const bf16*)gate, ldg, w, (bf16*)out, heads, dv, eps);
+  return KVCM_LAUNCH_RESULT();
+}

@@ -16,7 +16,11 @@ constexpr int TM = 64, TN = 64, TK = 16;   // block tile; 256 threads, each a 4x
 template <typename TIn, typename TOut>
 __global__ void __launch_bounds__(256)
 gemm_plain_kernel(const TIn* __restrict__ X, const TIn* __restrict__ W, TOut* __restrict__ Y,
-                  int M, int N, int K, int ldx, int ldw, int ldy) {
+                  int M, int N, int K, int ldx, int ldw, int ldy, long long bx, long long bw, long long by) {
+  // blockIdx.z: one product of a batch whose operands lie bx / bw / by elements apart
+  X += blockIdx.z * bx;
+  W += blockIdx.z * bw;
+  Y += blockIdx.z * by;
   __shared__ float xs[TK][TM + 1];
   __shared__ float ws[TK][TN + 1];
   const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
@@ -62,11 +66,12 @@ gemm_plain_kernel(const TIn* __restrict__ X, const TIn* __restrict__ W, TOut* __
 
 template <typename TIn, typename TOut>
 int launch_gemm_plain(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw,
-                      int ldy, cudaStream_t s) {
-  if (M == 0 || N == 0) return 0;
-  dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM);
+                      int ldy, cudaStream_t s, int batch = 1, long long bx = 0, long long bw = 0, long long by = 0) {
+  if (M == 0 || N == 0 || batch == 0) return 0;
+  if (batch < 0 || batch > 65535) return KVCM_ERR_UNSUPPORTED;
+  dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM, batch);
   gemm_plain_kernel<TIn, TOut><<<grid, 256, 0, s>>>((const TIn*)X, (const TIn*)W, (TOut*)Y, M, N, K,
-                                                    ldx, ldw, ldy);
+                                                    ldx, ldw, ldy, bx, bw, by);
   return KVCM_LAUNCH_RESULT();
 }
 
@@ -85,4 +90,15 @@ KVCM_API int kvcm_gemm_plain_bf16(const void* X, const void* W, void* Y, int M, 
 KVCM_API int kvcm_gemm_plain_bf16_f32out(const void* X, const void* W, void* Y, int M, int N, int K,
                                          int ldx, int ldw, int ldy, void* stream) {
   return launch_gemm_plain<bf16, float>(X, W, Y, M, N, K, ldx, ldw, ldy, (cudaStream_t)stream);
+}
+
+// A batch of such products in one launch (one per head, say): product z reads X + z*bx and
+// W + z*bw and writes Y + z*by (element counts); rows ldx / ldw / ldy apart as above.
+KVCM_API int kvcm_gemm_plain_batched_f32(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw,
+                                         int ldy, int batch, long long bx, long long bw, long long by, void* stream) {
+  return launch_gemm_plain<float, float>(X, W, Y, M, N, K, ldx, ldw, ldy, (cudaStream_t)stream, batch, bx, bw, by);
+}
+KVCM_API int kvcm_gemm_plain_batched_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw,
+                                          int ldy, int batch, long long bx, long long bw, long long by, void* stream) {
+  return launch_gemm_plain<bf16, bf16>(X, W, Y, M, N, K, ldx, ldw, ldy, (cudaStream_t)stream, batch, bx, bw, by);
 }

@@ -1,0 +1,351 @@
+// A feed-forward made of many small gated experts of which every row uses a few.
+//
+//   route    router logits in float (one warp a row), softmax over all experts, optionally only the
+//            experts of the best `keep` of `groups` equal groups of neighbours may be chosen (a
+//            group's score is its largest expert score), the `top` largest scores win; a row's
+//            weights are its chosen scores times `scale`, not renormalised.  An extra row of the
+//            router matrix, if present, is a per-row gate: sigmoid of its logit.
+//   sort     the (row, choice) pairs ordered by expert, cut into tiles of 64 pairs of one expert.
+//   gate_up  act[pair] = silu(h[row] Wg_e^T) * (h[row] Wu_e^T)      per tile, float accumulation
+//   down     y[pair]   = act[pair] Wd_e^T                           per tile, float results
+//   combine  out[row]  = sum_k weight[row, k] * y[row, k] + gate[row] * shared[row]   (float)
+//
+// Nothing is read on the host: counts and tile lists stay on the device and the product grids
+// are sized for the worst case (pairs / 64 + experts tiles), so a step can be recorded into a
+// CUDA graph.  Every output element is accumulated by one thread over k in ascending order, so
+// a row's result does not depend on what else is in the batch or on the order inside a tile.
+// Instantiated for float (the true 32-bit path: float FMAs only) and bfloat16 storage.
+#include "common.cuh"
+
+namespace kvcm {
+
+constexpr int MOE_TM = 64, MOE_TN = 64, MOE_TK = 16;
+
+__device__ __forceinline__ float moe_silu(float z) { return z / (1.f + expf(-z)); }
+
+// (value, index) maximum over a warp; the lower index wins a tie.  Every lane gets the result.
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+    if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+  }
+}
+
+// ------------------------------------------------------------------------------------ route
+template <typename T, typename W>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const T* __restrict__ h, int ldh, const W* __restrict__ wr, int rows, int D, int E, int G, int keep,
+                 int top, float scale, int has_gate, int* __restrict__ idx, float* __restrict__ wt,
+                 float* __restrict__ gate_out) {
+  extern __shared__ float route_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (row >= rows) return;
+  float* z = route_smem + size_t(warp) * (E + 1 + G);      // scores of the experts, then the gate's logit
+  float* gb = z + E + 1;                                    // best score of each group; -1 once kept
+  const T* hr = h + size_t(row) * ldh;
+  const int outs = E + (has_gate ? 1 : 0);
+  for (int e = 0; e < outs; ++e) {
+    const W* we = wr + size_t(e) * D;
+    float acc = 0.f;
+    for (int i = lane; i < D; i += 32) acc = fmaf(ldf(hr + i), ldf(we + i), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) z[e] = acc;
+  }
+  __syncwarp();
+  float m = -INFINITY;
+  for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
+  m = warp_max(m);
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) sum += expf(z[e] - m);
+  sum = warp_sum(sum);
+  __syncwarp();
+  for (int e = lane; e < E; e += 32) z[e] = expf(z[e] - m) / sum;
+  if (has_gate && lane == 0) gate_out[row] = 1.f / (1.f + expf(-z[E]));
+  __syncwarp();
+  const int per = E / G;
+  const bool limited = G > 1 && keep < G;
+  if (limited) {
+    for (int g = lane; g < G; g += 32) {
+      float best = 0.f;
+      for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, z[e]);
+      gb[g] = best;
+    }
+    __syncwarp();
+    for (int k = 0; k < keep; ++k) {
+      float bv = -1.f;
+      int bi = 0x7fffffff;
+      for (int g = lane; g < G; g += 32)
+        if (gb[g] > bv) { bv = gb[g]; bi = g; }
+      warp_argmax(bv, bi);
+      __syncwarp();
+      if (lane == 0 && bi < G) gb[bi] = -1.f;               // kept
+      __syncwarp();
+    }
+  }
+  for (int k = 0; k < top; ++k) {
+    float bv = -1.f;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const bool allowed = !limited || gb[e / per] < 0.f;
+      if (allowed && z[e] > bv) { bv = z[e]; bi = e; }
+    }
+    warp_argmax(bv, bi);
+    __syncwarp();
+    if (lane == 0) {
+      const bool ok = bi < E;
+      idx[size_t(row) * top + k] = ok ? bi : 0;
+      wt[size_t(row) * top + k] = ok ? bv * scale : 0.f;
+      if (ok) z[bi] = -2.f;                                  // taken
+    }
+    __syncwarp();
+  }
+}
+
+// ------------------------------------------------------------------------------------- sort
+// One block.  offsets[e] = first sorted place of expert e; pair_of[place] = row * top + k;
+// tiles: (expert, first place, pairs) for every 64 pairs of an expert; num_tiles[0] = how many.
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int* __restrict__ idx, int pairs, int E, int* __restrict__ offsets, int* __restrict__ pair_of,
+                int* __restrict__ tile_expert, int* __restrict__ tile_begin, int* __restrict__ tile_rows,
+                int* __restrict__ num_tiles) {
+  extern __shared__ int sort_smem[];
+  int* cnt = sort_smem;
+  int* cursor = sort_smem + E;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&cnt[idx[p]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      offsets[e] = at;
+      cursor[e] = at;
+      for (int b = 0; b < cnt[e]; b += MOE_TM, ++tiles) {
+        tile_expert[tiles] = e;
+        tile_begin[tiles] = at + b;
+        tile_rows[tiles] = min(MOE_TM, cnt[e] - b);
+      }
+      at += cnt[e];
+    }
+    offsets[E] = at;
+    num_tiles[0] = tiles;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) pair_of[atomicAdd(&cursor[idx[p]], 1)] = p;
+}
+
+// ----------------------------------------------------------------------------- the products
+// act[place, n] = silu(sum_k h[row, k] Wg[e][n, k]) * (sum_k h[row, k] Wu[e][n, k]);
+// wgu: [E, 2F, D], the F gate rows of an expert before its F up rows.
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_gate_up_kernel(const T* __restrict__ h, int ldh, const T* __restrict__ wgu, const int* __restrict__ pair_of,
+                   int top, const int* __restrict__ tile_expert, const int* __restrict__ tile_begin,
+                   const int* __restrict__ tile_rows, const int* __restrict__ num_tiles, T* __restrict__ act,
+                   int F, int D) {
+  const int tile = blockIdx.y;
+  if (tile >= num_tiles[0]) return;
+  __shared__ float xs[MOE_TK][MOE_TM + 1];
+  __shared__ float gsm[MOE_TK][MOE_TN + 1];
+  __shared__ float usm[MOE_TK][MOE_TN + 1];
+  __shared__ int src_row[MOE_TM];
+  const int e = tile_expert[tile], begin = tile_begin[tile], mrows = tile_rows[tile];
+  const int n0 = blockIdx.x * MOE_TN;
+  const T* Wg = wgu + size_t(e) * 2 * F * D;
+  const T* Wu = Wg + size_t(F) * D;
+  if (threadIdx.x < MOE_TM) src_row[threadIdx.x] = threadIdx.x < mrows ? pair_of[begin + threadIdx.x] / top : -1;
+  __syncthreads();
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+  float ag[4][4] = {}, au[4][4] = {};
+  for (int k0 = 0; k0 < D; k0 += MOE_TK) {
+    for (int i = threadIdx.x; i < MOE_TM * MOE_TK; i += 256) {
+      const int r = i / MOE_TK, c = i % MOE_TK;
+      const int src = src_row[r], gk = k0 + c;
+      xs[c][r] = (src >= 0 && gk < D) ? ldf(h + size_t(src) * ldh + gk) : 0.f;
+    }
+    for (int i = threadIdx.x; i < MOE_TN * MOE_TK; i += 256) {
+      const int r = i / MOE_TK, c = i % MOE_TK;
+      const int gn = n0 + r, gk = k0 + c;
+      const bool ok = gn < F && gk < D;
+      gsm[c][r] = ok ? ldf(Wg + size_t(gn) * D + gk) : 0.f;
+      usm[c][r] = ok ? ldf(Wu + size_t(gn) * D + gk) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < MOE_TK; ++k) {
+      float a[4], bg[4], bu[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = xs[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { bg[j] = gsm[k][tx * 4 + j]; bu[j] = usm[k][tx * 4 + j]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          ag[i][j] = fmaf(a[i], bg[j], ag[i][j]);
+          au[i][j] = fmaf(a[i], bu[j], au[i][j]);
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = ty * 4 + i;
+    if (m >= mrows) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gn = n0 + tx * 4 + j;
+      if (gn < F) stf(act + size_t(begin + m) * F + gn, moe_silu(ag[i][j]) * au[i][j]);
+    }
+  }
+}
+
+// y[pair, n] = sum_k act[place, k] Wd[e][n, k];  wd: [E, D, F];  y float, indexed by pair.
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_down_kernel(const T* __restrict__ act, const T* __restrict__ wd, const int* __restrict__ pair_of,
+                const int* __restrict__ tile_expert, const int* __restrict__ tile_begin,
+                const int* __restrict__ tile_rows, const int* __restrict__ num_tiles, float* __restrict__ y,
+                int F, int D) {
+  const int tile = blockIdx.y;
+  if (tile >= num_tiles[0]) return;
+  __shared__ float xs[MOE_TK][MOE_TM + 1];
+  __shared__ float ws[MOE_TK][MOE_TN + 1];
+  const int e = tile_expert[tile], begin = tile_begin[tile], mrows = tile_rows[tile];
+  const int n0 = blockIdx.x * MOE_TN;
+  const T* W = wd + size_t(e) * D * F;
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < F; k0 += MOE_TK) {
+    for (int i = threadIdx.x; i < MOE_TM * MOE_TK; i += 256) {
+      const int r = i / MOE_TK, c = i % MOE_TK;
+      const int gk = k0 + c;
+      xs[c][r] = (r < mrows && gk < F) ? ldf(act + size_t(begin + r) * F + gk) : 0.f;
+    }
+    for (int i = threadIdx.x; i < MOE_TN * MOE_TK; i += 256) {
+      const int r = i / MOE_TK, c = i % MOE_TK;
+      const int gn = n0 + r, gk = k0 + c;
+      ws[c][r] = (gn < D && gk < F) ? ldf(W + size_t(gn) * F + gk) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < MOE_TK; ++k) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = xs[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = ws[k][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = ty * 4 + i;
+    if (m >= mrows) continue;
+    const size_t pair = pair_of[begin + m];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gn = n0 + tx * 4 + j;
+      if (gn < D) y[pair * D + gn] = acc[i][j];
+    }
+  }
+}
+
+// out[row, i] = sum_k wt[row, k] * y[row * top + k, i]  (+ gate[row] * shared[row, i])
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ wt, int top, const float* __restrict__ shared_y,
+                   const float* __restrict__ gate, float* __restrict__ out, int D) {
+  const int row = blockIdx.x;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k) acc = fmaf(wt[size_t(row) * top + k], y[(size_t(row) * top + k) * D + i], acc);
+    if (shared_y) acc += (gate ? gate[row] : 1.f) * shared_y[size_t(row) * D + i];
+    out[size_t(row) * D + i] = acc;
+  }
+}
+
+template <typename T>
+int launch_moe_route(const void* h, int ldh, const void* wr, int w_f32, int rows, int D, int E, int G, int keep, int top,
+                     float scale, int has_gate, int* idx, float* wt, float* gate_out, cudaStream_t s) {
+  if (rows == 0) return 0;
+  if (E < 1 || G < 1 || E % G || keep < 1 || keep > G || top < 1 || top > (E / G) * keep) return KVCM_ERR_UNSUPPORTED;
+  const int warps = 4;
+  const size_t smem = size_t(warps) * (E + 1 + G) * sizeof(float);
+  if (smem > 48 * 1024) return KVCM_ERR_UNSUPPORTED;
+  const int blocks = (rows + warps - 1) / warps;
+  if (w_f32)
+    moe_route_kernel<T, float><<<blocks, warps * 32, smem, s>>>((const T*)h, ldh, (const float*)wr, rows, D, E, G, keep,
+                                                               top, scale, has_gate, idx, wt, gate_out);
+  else
+    moe_route_kernel<T, T><<<blocks, warps * 32, smem, s>>>((const T*)h, ldh, (const T*)wr, rows, D, E, G, keep, top,
+                                                           scale, has_gate, idx, wt, gate_out);
+  return KVCM_LAUNCH_RESULT();
+}
+
+template <typename T>
+int launch_moe_experts(const void* h, int ldh, const void* wgu, const void* wd, const int* idx, int rows, int top, int E,
+                       int F, int D, int* work, void* act, float* y, cudaStream_t s) {
+  if (rows == 0) return 0;
+  const int pairs = rows * top;
+  const int max_tiles = pairs / MOE_TM + E;
+  if (max_tiles > 65535 || size_t(2 * E) * sizeof(int) > 48 * 1024) return KVCM_ERR_UNSUPPORTED;
+  // work: offsets[E + 1] | num_tiles[1] | pair_of[pairs] | tile_expert, tile_begin, tile_rows [max_tiles each]
+  int* offsets = work;
+  int* num_tiles = work + E + 1;
+  int* pair_of = num_tiles + 1;
+  int* tile_expert = pair_of + pairs;
+  int* tile_begin = tile_expert + max_tiles;
+  int* tile_rows = tile_begin + max_tiles;
+  moe_sort_kernel<<<1, 1024, size_t(2 * E) * sizeof(int), s>>>(idx, pairs, E, offsets, pair_of, tile_expert, tile_begin,
+                                                               tile_rows, num_tiles);
+  int rc = KVCM_LAUNCH_RESULT();
+  if (rc) return rc;
+  moe_gate_up_kernel<T><<<dim3((F + MOE_TN - 1) / MOE_TN, max_tiles), 256, 0, s>>>(
+      (const T*)h, ldh, (const T*)wgu, pair_of, top, tile_expert, tile_begin, tile_rows, num_tiles, (T*)act, F, D);
+  rc = KVCM_LAUNCH_RESULT();
+  if (rc) return rc;
+  moe_down_kernel<T><<<dim3((D + MOE_TN - 1) / MOE_TN, max_tiles), 256, 0, s>>>(
+      (const T*)act, (const T*)wd, pair_of, tile_expert, tile_begin, tile_rows, num_tiles, y, F, D);
+  return KVCM_LAUNCH_RESULT();
+}
+
+}  // namespace kvcm
+
+using namespace kvcm;
+
+// Ints of scratch that kvcm_moe_experts_* needs for `rows` rows.
+KVCM_API long long kvcm_moe_work_ints(int rows, int top, int E) {
+  const long long pairs = (long long)rows * top;
+  return (E + 2) + pairs + 3 * (pairs / MOE_TM + E);
+}
+
+#define KVCM_MOE(SUFFIX, T)                                                                                          \
+  KVCM_API int kvcm_moe_route_##SUFFIX(const void* h, int ldh, const void* wr, int w_f32, int rows, int D, int E,    \
+                                       int G, int keep, int top, float scale, int has_gate, int* idx, float* wt,     \
+                                       float* gate_out, void* stream) {                                              \
+    return launch_moe_route<T>(h, ldh, wr, w_f32, rows, D, E, G, keep, top, scale, has_gate, idx, wt, gate_out,      \
+                               (cudaStream_t)stream);                                                                \
+  }                                                                                                                  \
+  KVCM_API int kvcm_moe_experts_##SUFFIX(const void* h, int ldh, const void* wgu, const void* wd, const int* idx,    \
+                                         int rows, int top, int E, int F, int D, int* work, void* act, float* y,     \
+                                         void* stream) {                                                             \
+    return launch_moe_experts<T>(h, ldh, wgu, wd, idx, rows, top, E, F, D, work, act, y, (cudaStream_t)stream);      \
+  }
+
+KVCM_MOE(f32, float)
+KVCM_MOE(bf16, bf16)
+
+KVCM_API int kvcm_moe_combine(const float* y, const float* wt, int top, const float* shared_y, const float* gate,
+                              float* out, int rows, int D, void* stream) {
+  if (rows == 0) return 0;
+  moe_combine_kernel<float><<<rows, 256, 0, (cudaStream_t)stream>>>(y, wt, top, shared_y, gate, out, D);
+  return KVCM_LAUNCH_RESULT();
+}

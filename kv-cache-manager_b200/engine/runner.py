@@ -128,7 +128,8 @@ class ModelRunner:
             tile_seq=view(layout.off_tile_seq, max(layout.prefill_tiles, 0)),
             tile_q0=view(layout.off_tile_q0, max(layout.prefill_tiles, 0)),
             logit_rows=view(layout.off_logit_rows, layout.logit_rows),
-            groups=groups, dtype=self.dtype, workspace=self, options=self.options)
+            groups=groups, dtype=self.dtype, workspace=self, options=self.options,
+            prev_tokens=view(layout.off_prev_tokens, T))
 
     # ------------------------------------------------------------------------- forward
     def forward(self, ctx: StepContext) -> Optional[torch.Tensor]:

@@ -864,3 +864,199 @@ def forward(args: ForwardArgs) -> int:
         raise KernelError(f"forward: sizes not supported (rows {args.rows}, hidden {args.H}, heads {args.nh}/{args.nkv} "
                           f"of {args.hd})")
     raise KernelError(f"forward: error {rc} at a launch (rows {args.rows})")
+
+
+# ------------------------------------------------ kernels around an output-normed residual stream
+
+def _ll(v) -> ctypes.c_longlong:
+    return ctypes.c_longlong(int(v))
+
+
+def embed_sum(ids: torch.Tensor, prev: Optional[torch.Tensor], positions: torch.Tensor, table: torch.Tensor,
+              pair: Optional[torch.Tensor], place: Optional[torch.Tensor], x: torch.Tensor,
+              h: Optional[torch.Tensor], buckets: int = 0, mul_prev: int = 0, mul_cur: int = 0) -> None:
+    """x[t] = table[id] + pair[(prev*mul_prev + id*mul_cur) % buckets, or row `buckets` without an earlier
+    token] + place[position]; x float32 [T, H]; ``h`` (optional) the same rows in the tables' dtype."""
+    _cuda(ids, prev, positions, table, pair, place, x, h)
+    T, H = x.shape
+    _need(ids.dtype == _I32 and positions.dtype == _I32 and ids.numel() >= T and positions.numel() >= T,
+          "embed_sum: ids/positions int32 [T]")
+    _need(x.dtype == torch.float32 and x.is_contiguous() and table.is_contiguous() and table.shape[1] == H, "embed_sum: layout")
+    for t in (pair, place):
+        _need(t is None or (t.dtype == table.dtype and t.is_contiguous() and t.shape[1] == H), "embed_sum: tables differ")
+    _need(pair is None or (prev is not None and prev.dtype == _I32 and prev.numel() >= T and pair.shape[0] == buckets + 1),
+          "embed_sum: the pair table needs buckets + 1 rows and the rows' previous tokens")
+    _need(h is None or (h.dtype == table.dtype and h.is_contiguous() and h.shape == x.shape), "embed_sum: h")
+    fn = getattr(_lib(), "kvcm_embed_sum_" + _suffix(table))
+    _check(fn(_p(ids), _p(prev), _p(positions), _p(table), _p(pair), _p(place), _p(x), _p(h), T, H, table.shape[0],
+              int(buckets), _ll(mul_prev), _ll(mul_cur), place.shape[0] if place is not None else 0, _stream()), "embed_sum")
+
+
+def rms_scale_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, h: Optional[torch.Tensor],
+                  eps: float, mult: float) -> None:
+    """x += mult * weight * y / sqrt(mean(y^2) + eps) row by row (x float32, y float32 or the storage
+    dtype); ``h`` (optional, storage dtype) receives the new rows of x."""
+    _cuda(x, y, weight, h)
+    T, H = x.shape
+    _need(x.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and y.shape == x.shape
+          and weight.numel() == H, "rms_scale_add: shapes")
+    store = h.dtype if h is not None else (y.dtype if y.dtype != torch.float32 else weight.dtype)
+    _need(y.dtype in (torch.float32, store) and weight.dtype in (torch.float32, store), "rms_scale_add: dtypes")
+    _need(h is None or (h.is_contiguous() and h.shape == x.shape), "rms_scale_add: h")
+    fn = getattr(_lib(), "kvcm_rms_scale_add_" + _SUFFIX[store])
+    _check(fn(_p(x), _p(y), int(y.dtype == torch.float32), _p(weight), int(weight.dtype == torch.float32), _p(h),
+              T, H, ctypes.c_float(eps), ctypes.c_float(mult), _stream()), "rms_scale_add", f"(hidden={H})")
+
+
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    _cuda(x, out)
+    _need(x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and x.shape == out.shape, "cast_rows: layout")
+    fn = getattr(_lib(), "kvcm_cast_rows_" + _suffix(out))
+    _check(fn(_p(x), _p(out), _ll(x.numel()), _stream()), "cast_rows")
+
+
+def gemm_plain_batched(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
+    """y[m, b, :] = x[m, b, :] @ w[b]^T for every b: x [M, B, K] (rows and heads may be strided, K dense),
+    w [B, N, K] contiguous, y [M, B, N] (K-dense too).  Plain kernel, float accumulation in a fixed order."""
+    _cuda(x, w, y)
+    M, B, K = x.shape
+    N = w.shape[1]
+    _need(w.shape == (B, N, K) and w.is_contiguous() and y.shape == (M, B, N), "gemm_plain_batched: shapes")
+    _need(x.stride(2) == 1 and y.stride(2) == 1 and x.dtype == w.dtype == y.dtype, "gemm_plain_batched: layout")
+    fn = getattr(_lib(), "kvcm_gemm_plain_batched_" + _suffix(x))
+    _check(fn(_p(x), _p(w), _p(y), M, N, K, x.stride(0), K, y.stride(0), B, _ll(x.stride(1)), _ll(N * K),
+              _ll(y.stride(1)), _stream()), "gemm_plain_batched")
+
+
+# ------------------------------------------------------------------------ the gated delta rule
+
+def delta_scan_max_dk() -> int:
+    return int(_lib().kvcm_delta_scan_max_dk())
+
+
+def delta_conv(proj: torch.Tensor, conv_w: torch.Tensor, state: torch.Tensor, conv_off: int, ctx,
+               out: torch.Tensor) -> None:
+    """Causal convolution over time + SiLU of the first ``channels`` columns of ``proj`` into float32
+    ``out`` [T, channels]; earlier inputs come from (and the newest go to) the requests' state rows."""
+    _cuda(proj, conv_w, state, out)
+    T, C = out.shape
+    taps = conv_w.shape[1]
+    _need(conv_w.dtype == torch.float32 and conv_w.is_contiguous() and conv_w.shape[0] == C, "delta_conv: taps [channels, taps] float32")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and proj.stride(1) == 1 and proj.shape[1] >= C, "delta_conv: layout")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and state.dim() == 2
+          and state.shape[1] >= conv_off + (taps - 1) * C, "delta_conv: state rows too short")
+    fn = getattr(_lib(), "kvcm_delta_conv_" + _suffix(proj))
+    _check(fn(_p(proj), proj.stride(0), _p(conv_w), taps, _p(state), _ll(state.stride(0)), _ll(conv_off), _p(ctx.row_seq),
+              _p(ctx.seq_q_start), _p(ctx.seq_q_len), _p(ctx.seq_state_slot), _p(out), T, ctx.seqs, C, _stream()), "delta_conv")
+    if taps > 1:
+        global _launches
+        _launches += 1                      # the state update
+
+
+def delta_prepare(qkv: torch.Tensor, ba: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+                  heads: int, qk_heads: int, dk: int) -> None:
+    """In place: query and key heads of ``qkv`` to unit length (queries also times dk^-1/2);
+    ``ba`` = [b | a] becomes [sigmoid(b) | exp(-exp(A_log) softplus(a + dt_bias))]."""
+    _cuda(qkv, ba, a_log, dt_bias)
+    _need(all(t.dtype == torch.float32 and t.is_contiguous() for t in (qkv, ba, a_log, dt_bias)), "delta_prepare: float32")
+    _need(ba.shape == (qkv.shape[0], 2 * heads) and a_log.numel() == heads and dt_bias.numel() == heads
+          and qkv.shape[1] >= 2 * qk_heads * dk, "delta_prepare: shapes")
+    _check(_lib().kvcm_delta_prepare(_p(qkv), qkv.shape[1], _p(ba), _p(a_log), _p(dt_bias), qkv.shape[0], heads, qk_heads,
+                                     dk, _stream()), "delta_prepare")
+
+
+def delta_scan(qkv: torch.Tensor, bg: torch.Tensor, state: torch.Tensor, ctx, out: torch.Tensor,
+               heads: int, qk_heads: int, dk: int, dv: int) -> None:
+    """The recurrence over every request's rows of the step, from and into its state row."""
+    _cuda(qkv, bg, state, out)
+    _need(all(t.dtype == torch.float32 and t.is_contiguous() for t in (qkv, bg, state, out)), "delta_scan: float32")
+    _need(qkv.shape[1] == 2 * qk_heads * dk + heads * dv and out.shape == (qkv.shape[0], heads * dv)
+          and state.shape[1] >= heads * dk * dv, "delta_scan: shapes")
+    _check(_lib().kvcm_delta_scan(_p(qkv), qkv.shape[1], _p(bg), _p(state), _ll(state.stride(0)), _p(ctx.seq_q_start),
+                                  _p(ctx.seq_q_len), _p(ctx.seq_state_slot), _p(out), ctx.seqs, heads, qk_heads, dk, dv,
+                                  _stream()), "delta_scan", f"(dk={dk}, dv={dv})")
+
+
+def gated_rms(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, heads: int,
+              dv: int, eps: float) -> None:
+    """out[t, h, :] = o[t, h, :] / rms * weight * silu(gate[t, h, :]); o float32, gate/out storage dtype."""
+    _cuda(o, gate, weight, out)
+    T = o.shape[0]
+    _need(o.dtype == torch.float32 and o.is_contiguous() and o.shape == (T, heads * dv) and out.is_contiguous()
+          and out.shape == o.shape and gate.stride(1) == 1 and gate.shape[1] >= heads * dv and gate.dtype == out.dtype
+          and weight.dtype == torch.float32 and weight.numel() == dv, "gated_rms: layout")
+    fn = getattr(_lib(), "kvcm_gated_rms_" + _suffix(out))
+    _check(fn(_p(o), _p(gate), gate.stride(0), _p(weight), _p(out), T, heads, dv, ctypes.c_float(eps), _stream()), "gated_rms")
+
+
+# ----------------------------------------------------------------------------- latent cache
+
+def latent_norm_cache(v: torch.Tensor, weight: torch.Tensor, slot_mapping: torch.Tensor, cache: torch.Tensor,
+                      eps: float) -> None:
+    """cache[slot of row] = weight * v[row] / sqrt(mean(v[row]^2) + eps); cache [pages, 1, page, width]."""
+    _cuda(v, weight, slot_mapping, cache)
+    T, R = v.shape
+    _need(v.stride(1) == 1 and v.dtype == cache.dtype and cache.is_contiguous() and cache.shape[1] == 1
+          and cache.shape[3] == R, "latent_norm_cache: layout")
+    _need(weight.dtype == torch.float32 and weight.numel() == R and slot_mapping.dtype == _I32
+          and slot_mapping.numel() >= T, "latent_norm_cache: weight float32 [width], slots int32 [T]")
+    fn = getattr(_lib(), "kvcm_latent_norm_cache_" + _suffix(v))
+    _check(fn(_p(v), v.stride(0), _p(weight), _p(slot_mapping), _p(cache), T, R, ctypes.c_float(eps), _stream()),
+           "latent_norm_cache")
+
+
+# ---------------------------------------------------------------------------- routed experts
+
+def moe_route(h: torch.Tensor, router: torch.Tensor, experts: int, groups: int, keep: int, top: int, scale: float,
+              idx: torch.Tensor, wt: torch.Tensor, gate: Optional[torch.Tensor]) -> None:
+    """Per row: float32 router logits, softmax, group-limited choice of ``top`` experts; ``idx`` int32
+    [T, top], ``wt`` float32 [T, top] = score * scale; ``gate`` float32 [T] = sigmoid of the logit of
+    the router matrix's extra row (row ``experts``)."""
+    _cuda(h, router, idx, wt, gate)
+    T, D = h.shape
+    _need(h.stride(1) == 1 and router.is_contiguous() and router.shape == (experts + (gate is not None), D)
+          and router.dtype in (torch.float32, h.dtype), "moe_route: router [experts (+1), width]")
+    _need(idx.dtype == _I32 and idx.is_contiguous() and idx.shape == (T, top) and wt.dtype == torch.float32
+          and wt.is_contiguous() and wt.shape == (T, top), "moe_route: outputs")
+    _need(gate is None or (gate.dtype == torch.float32 and gate.numel() >= T), "moe_route: gate float32 [T]")
+    fn = getattr(_lib(), "kvcm_moe_route_" + _suffix(h))
+    _check(fn(_p(h), h.stride(0), _p(router), int(router.dtype == torch.float32), T, D, experts, groups, keep, top,
+              ctypes.c_float(scale), int(gate is not None), _p(idx), _p(wt), _p(gate), _stream()), "moe_route",
+           f"(experts={experts}, groups={groups}, keep={keep}, top={top})")
+
+
+def moe_work_ints(rows: int, top: int, experts: int) -> int:
+    return int(_lib().kvcm_moe_work_ints(int(rows), int(top), int(experts)))
+
+
+def moe_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, idx: torch.Tensor,
+                work: torch.Tensor, act: torch.Tensor, y: torch.Tensor) -> None:
+    """y[t * top + k] = expert idx[t, k] applied to h[t] (float32 [T * top, D]); w_gate_up [E, 2F, D]
+    (gate rows before up rows), w_down [E, D, F]; act [T * top, F] and work int32 are scratch."""
+    _cuda(h, w_gate_up, w_down, idx, work, act, y)
+    T, D = h.shape
+    top = idx.shape[1]
+    E, F2, _ = w_gate_up.shape
+    F = F2 // 2
+    _need(w_gate_up.is_contiguous() and w_down.is_contiguous() and w_gate_up.shape == (E, 2 * F, D)
+          and w_down.shape == (E, D, F) and w_gate_up.dtype == h.dtype == w_down.dtype == act.dtype, "moe_experts: weights")
+    _need(h.stride(1) == 1 and act.is_contiguous() and act.shape == (T * top, F) and y.dtype == torch.float32
+          and y.is_contiguous() and y.shape == (T * top, D), "moe_experts: buffers")
+    _need(work.dtype == _I32 and work.numel() >= moe_work_ints(T, top, E), "moe_experts: work too small")
+    fn = getattr(_lib(), "kvcm_moe_experts_" + _suffix(h))
+    _check(fn(_p(h), h.stride(0), _p(w_gate_up), _p(w_down), _p(idx), T, top, E, F, D, _p(work), _p(act), _p(y), _stream()),
+           "moe_experts", f"(experts={E}, ff={F})")
+    global _launches
+    _launches += 2                          # sort, gate/up, down
+
+
+def moe_combine(y: torch.Tensor, wt: torch.Tensor, shared_y: Optional[torch.Tensor], gate: Optional[torch.Tensor],
+                out: torch.Tensor) -> None:
+    """out[t] = sum_k wt[t, k] * y[t * top + k] + gate[t] * shared_y[t]; all float32."""
+    _cuda(y, wt, shared_y, gate, out)
+    T, D = out.shape
+    top = wt.shape[1]
+    _need(all(t is None or (t.dtype == torch.float32 and t.is_contiguous()) for t in (y, wt, shared_y, gate, out)),
+          "moe_combine: float32")
+    _need(y.shape == (T * top, D) and (shared_y is None or shared_y.shape == (T, D)), "moe_combine: shapes")
+    _check(_lib().kvcm_moe_combine(_p(y), _p(wt), top, _p(shared_y), _p(gate), _p(out), T, D, _stream()), "moe_combine")

@@ -1,5 +1,5 @@
 """Architectures assembled from parts.  Importing this package registers them."""
 from .spec import ModelSpec, TensorBinding
-from . import llama
+from . import llama, tolanex
 
-__all__ = ["ModelSpec", "TensorBinding", "llama"]
+__all__ = ["ModelSpec", "TensorBinding", "llama", "tolanex"]

@@ -3,17 +3,21 @@ from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, Blo
                    FeedForward, GroupView, LayerCall, Mixer, Norm, ParamSpec, Part,
                    PositionEncoding, Registry, SiteCache, StateSpec, StepContext)
 from .linear import Linear, matmul_nt
-from .norm import RMSNorm
+from .norm import OutputRMSNorm, RMSNorm
 from .rope import NoPositionEncoding, RotaryEmbedding
 from .attention import PagedAttention
+from .delta import GatedDeltaMixer
+from .latent_attention import LatentAttention
 from .mlp import GatedMLP
-from .embedding import Embedding, LMHead
-from .block import PreNormBlock
+from .moe import RoutedExperts
+from .embedding import Embedding, LMHead, SummedEmbedding
+from .block import OutputNormBlock, PreNormBlock
 
 __all__ = [
     "BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITION_ENCODINGS", "Block", "CacheSpec",
     "FeedForward", "GroupView", "LayerCall", "Mixer", "Norm", "ParamSpec", "Part",
     "PositionEncoding", "Registry", "SiteCache", "StateSpec", "StepContext", "Linear", "matmul_nt",
     "RMSNorm", "NoPositionEncoding", "RotaryEmbedding", "PagedAttention", "GatedMLP", "Embedding",
-    "LMHead", "PreNormBlock",
+    "LMHead", "PreNormBlock", "OutputRMSNorm", "OutputNormBlock", "SummedEmbedding", "GatedDeltaMixer",
+    "LatentAttention", "RoutedExperts",
 ]

@@ -108,6 +108,7 @@ class CacheSpec:
     num_kv_heads: int
     head_dim: int
     window: int = 0                 # 0: every key is kept; w: only the last w positions
+    values: bool = True             # False: one pool only (a mixer that derives keys AND values from what it caches)
 
 
 @dataclass(frozen=True)
@@ -144,7 +145,7 @@ class SiteCache:
     its state slab."""
     group: int = -1
     k: Optional[torch.Tensor] = None        # [pages, nkv, block, hd]
-    v: Optional[torch.Tensor] = None
+    v: Optional[torch.Tensor] = None        # None when the group's spec keeps no values
     writes: bool = True
     state: Optional[torch.Tensor] = None    # [slots, *shape]
 
@@ -176,6 +177,9 @@ class StepContext:
     dtype: torch.dtype               # storage dtype of activations
     workspace: Any = None            # per-engine scratch provider (see engine.runner.Workspace)
     options: Dict[str, Any] = field(default_factory=dict)
+    prev_tokens: Optional[torch.Tensor] = None   # per row: the request's token one position earlier (-1 at position 0)
+    h_stream: Optional[torch.Tensor] = None      # storage-dtype copy of the residual stream, kept current by blocks
+                                                 # whose sublayers read the stream itself (None: nobody keeps one)
 
 
 # ------------------------------------------------------------------------------ registries

@@ -1,12 +1,15 @@
 """Arrangement of parts in one layer.  ``PreNormBlock``: x += mixer(norm1(x)); x += ffn(norm2(x))
 (``src/model/llama.cpp:104-124``).  The residual stream x is float32; a sub-layer's output is
-not added at once but handed on as *pending* and added inside the next norm kernel."""
+not added at once but handed on as *pending* and added inside the next norm kernel.
+``OutputNormBlock``: x += m * norm1(mixer(x)); x += m * norm2(ffn(x)): the sublayers read the
+stream itself and the norms sit on their outputs; nothing is left pending."""
 from __future__ import annotations
 
 from typing import Optional
 
 import torch
 
+from ..kernels import library as K
 from .base import BLOCKS, Block, FeedForward, Mixer, Norm, SiteCache, StepContext
 
 
@@ -26,3 +29,38 @@ class PreNormBlock(Block):
         y = self.mixer.forward(h, ctx, site)
         self.norm2.forward(x, y, h)
         return self.ffn.forward(h, ctx)
+
+
+@BLOCKS.register("output_norm")
+class OutputNormBlock(Block):
+    """``norm1`` / ``norm2`` are norms of the "rmsnorm_output" kind (they own the residual add and the
+    multiplier).  ``ffn`` may be None: a layer of a mixer only.  The sublayers read the stream in the
+    storage dtype: with float32 storage that is x itself, else a copy ``ctx.h_stream`` that the norm
+    kernels keep current (the embedding may have left one; otherwise the first block makes it)."""
+
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm] = None,
+                 ffn: Optional[FeedForward] = None) -> None:
+        super().__init__()
+        self.norm1 = self.add_child("norm1", norm1)
+        self.mixer = self.add_child("mixer", mixer)
+        self.norm2 = self.add_child("norm2", norm2) if norm2 is not None else None
+        self.ffn = self.add_child("ffn", ffn) if ffn is not None else None
+        if (self.norm2 is None) != (self.ffn is None):
+            raise ValueError("output_norm block: a feed-forward and its norm come together")
+
+    def forward(self, x: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
+                site: SiteCache) -> Optional[torch.Tensor]:
+        if pending is not None:
+            K.add_residual(x, pending)
+        if ctx.dtype == torch.float32:
+            h = keep = None
+        else:
+            h = ctx.h_stream
+            if h is None:
+                h = ctx.h_stream = torch.empty(x.shape, dtype=ctx.dtype, device=x.device)
+                K.cast_rows(x, h)
+            keep = h
+        self.norm1.forward(x, self.mixer.forward(x if h is None else h, ctx, site), keep)
+        if self.ffn is not None:
+            self.norm2.forward(x, self.ffn.forward(x if h is None else h, ctx), keep)
+        return None

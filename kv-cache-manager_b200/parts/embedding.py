@@ -24,6 +24,35 @@ class Embedding(Part):
         return x
 
 
+class SummedEmbedding(Part):
+    """A sum of tables into the float32 residual stream: the token's row; optionally the row of a
+    hashed table for the pair (previous token, token), row ``(prev * mul_prev + token * mul_cur) mod
+    buckets`` and the extra last row ``buckets`` for a request's first token; optionally a learned
+    row per position (not scaled).  The previous token comes with the batch (the request keeps its
+    tokens), so it survives portions, batching and eviction like the tokens themselves."""
+
+    def __init__(self, vocab: int, hidden: int, buckets: int = 0, mul_prev: int = 0, mul_cur: int = 0,
+                 max_positions: int = 0) -> None:
+        super().__init__()
+        self.vocab, self.hidden = vocab, hidden
+        self.buckets, self.mul_prev, self.mul_cur, self.max_positions = int(buckets), int(mul_prev), int(mul_cur), int(max_positions)
+        self.declare("weight", (vocab, hidden), ("normal", 0.02), "table")
+        if self.buckets:
+            self.declare("pair", (self.buckets + 1, hidden), ("normal", 0.02), "table")
+        if self.max_positions:
+            self.declare("place", (self.max_positions, hidden), ("normal", 0.02), "table")
+
+    def forward(self, ctx: StepContext) -> torch.Tensor:
+        table = self.param("weight")
+        x = torch.empty((ctx.rows, self.hidden), dtype=torch.float32, device=ctx.tokens.device)
+        h = None
+        if ctx.dtype != torch.float32 and table.dtype == ctx.dtype:
+            h = ctx.h_stream = torch.empty((ctx.rows, self.hidden), dtype=ctx.dtype, device=x.device)
+        K.embed_sum(ctx.tokens, ctx.prev_tokens, ctx.positions, table, self.param("pair") if self.buckets else None,
+                    self.param("place") if self.max_positions else None, x, h, self.buckets, self.mul_prev, self.mul_cur)
+        return x
+
+
 class LMHead(Part):
     """logits = h W^T in float32.  ``weight`` may alias the embedding table (tied)."""
 

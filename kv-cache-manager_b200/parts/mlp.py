@@ -21,7 +21,7 @@ class GatedMLP(FeedForward):
         self.gate_up = self.add_child("gate_up", Linear(hidden, 2 * intermediate))
         self.down = self.add_child("down", Linear(intermediate, hidden))
 
-    def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+    def forward(self, h: torch.Tensor, ctx: StepContext, out_dtype=None) -> torch.Tensor:
         act = torch.empty((h.shape[0], self.intermediate), dtype=h.dtype, device=h.device)
         w = self.gate_up.param("weight")
         # A handful of rows (decode): the gate/up product and the activation in one kernel (the
@@ -48,4 +48,4 @@ class GatedMLP(FeedForward):
                 K.gate_up_silu_tcgen05(h, w, act)
         else:
             K.silu_mul(self.gate_up.forward(h, ctx), act)
-        return self.down.forward(act, ctx)
+        return self.down.forward(act, ctx, out_dtype)
