@@ -23,7 +23,10 @@ embed_sum_kernel(const int* __restrict__ ids, const int* __restrict__ prev, cons
   const int pos = positions[t];
   const bool bad = id < 0 || id >= vocab || (place && pos >= max_pos);
   long long row = buckets;
-  if (pair && prev[t] >= 0) row = ((long long)prev[t] * mul_prev + (long long)id * mul_cur) % buckets;
+  if (pair && prev[t] >= 0) {
+    row = ((long long)prev[t] * mul_prev + (long long)id * mul_cur) % buckets;
+    if (row < 0) row += buckets;                          // the mathematical residue, also for negative multipliers
+  }
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float v;
     if (bad) {

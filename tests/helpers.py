@@ -140,13 +140,13 @@ class Replayer:
         never = sorted(set(range(self.kv.num_blocks())) - set(self.pages_seen))
         bad = []
         for page in never:
-            if any(bool(t[:, page].count_nonzero()) for t in (pools.k[0], pools.v[0])):
+            if any(bool(t[:, page].count_nonzero()) for t in (pools.k[0], pools.v[0]) if t is not None):
                 bad.append(page)
         return bad
 
 
 def run_trace_tool(folder: str, dtype: str, steps: List[dict], max_tokens: int, out_dir: str,
-                   extra: Sequence[str] = ()) -> Dict[int, np.ndarray]:
+                   extra: Sequence[str] = (), vocab_key: str = "vocab_size") -> Dict[int, np.ndarray]:
     """Runs bin/trace_run as a user would and returns {step: float32 [wanted, vocab]}."""
     cfg = json.load(open(os.path.join(folder, "config.json")))
     text = "".join(json.dumps(s) + "\n" for s in steps)
@@ -162,7 +162,7 @@ def run_trace_tool(folder: str, dtype: str, steps: List[dict], max_tokens: int, 
         wanted = sum(len(e.get("want", [])) for e in s["entries"])
         if wanted:
             a = np.fromfile(f, dtype="<f4")
-            out[s["step"]] = a.reshape(wanted, cfg["vocab_size"])
+            out[s["step"]] = a.reshape(wanted, cfg[vocab_key])
         else:
             assert not os.path.exists(f)
     return out
