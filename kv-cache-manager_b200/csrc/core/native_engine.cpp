@@ -13,7 +13,7 @@ namespace {
 constexpr int kBatchBuckets[] = {1, 2, 4, 8, 16, 32, 64, 128, 256, 512};
 constexpr int kMinCtxBucket = 256;
 const char* const kFamilies[] = {"gemm_stream", "gemm_tcgen05", "gemm_tcgen05_pair", "gemm_tcgen05_splitk",
-                                 "attention_tcgen05"};
+                                 "attention_tcgen05", "moe_tcgen05"};
 }  // namespace
 
 int NativeEngine::batch_bucket(int n) {

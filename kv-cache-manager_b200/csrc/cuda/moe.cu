@@ -9,6 +9,8 @@
 //   gate_up  act[pair] = silu(h[row] Wg_e^T) * (h[row] Wu_e^T)      per tile, float accumulation
 //   down     y[pair]   = act[pair] Wd_e^T                           per tile, float results
 //   combine  out[row]  = sum_k weight[row, k] * y[row, k] + gate[row] * shared[row]   (float)
+// (bfloat16 rows whose sizes allow it take the tensor-core form of the two products,
+// csrc/cuda/moe_tcgen05.cu, after the same sort into tiles of 128.)
 //
 // Nothing is read on the host: counts and tile lists stay on the device and the product grids
 // are sized for the worst case (pairs / 64 + experts tiles), so a step can be recorded into a
@@ -105,12 +107,13 @@ moe_route_kernel(const T* __restrict__ h, int ldh, const W* __restrict__ wr, int
 }
 
 // ------------------------------------------------------------------------------------- sort
-// One block.  offsets[e] = first sorted place of expert e; pair_of[place] = row * top + k;
-// tiles: (expert, first place, pairs) for every 64 pairs of an expert; num_tiles[0] = how many.
+// One block.  offsets[e] = first sorted place of expert e; pair_of[place] = row * top + k and
+// place_of[row * top + k] = place; tiles: (expert, first place, pairs) for every `tile_m` pairs of an
+// expert; num_tiles[0] = how many.
 __global__ void __launch_bounds__(1024)
-moe_sort_kernel(const int* __restrict__ idx, int pairs, int E, int* __restrict__ offsets, int* __restrict__ pair_of,
-                int* __restrict__ tile_expert, int* __restrict__ tile_begin, int* __restrict__ tile_rows,
-                int* __restrict__ num_tiles) {
+moe_sort_kernel(const int* __restrict__ idx, int pairs, int E, int tile_m, int* __restrict__ offsets,
+                int* __restrict__ pair_of, int* __restrict__ place_of, int* __restrict__ tile_expert,
+                int* __restrict__ tile_begin, int* __restrict__ tile_rows, int* __restrict__ num_tiles) {
   extern __shared__ int sort_smem[];
   int* cnt = sort_smem;
   int* cursor = sort_smem + E;
@@ -123,10 +126,10 @@ moe_sort_kernel(const int* __restrict__ idx, int pairs, int E, int* __restrict__
     for (int e = 0; e < E; ++e) {
       offsets[e] = at;
       cursor[e] = at;
-      for (int b = 0; b < cnt[e]; b += MOE_TM, ++tiles) {
+      for (int b = 0; b < cnt[e]; b += tile_m, ++tiles) {
         tile_expert[tiles] = e;
         tile_begin[tiles] = at + b;
-        tile_rows[tiles] = min(MOE_TM, cnt[e] - b);
+        tile_rows[tiles] = min(tile_m, cnt[e] - b);
       }
       at += cnt[e];
     }
@@ -134,7 +137,11 @@ moe_sort_kernel(const int* __restrict__ idx, int pairs, int E, int* __restrict__
     num_tiles[0] = tiles;
   }
   __syncthreads();
-  for (int p = threadIdx.x; p < pairs; p += blockDim.x) pair_of[atomicAdd(&cursor[idx[p]], 1)] = p;
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int place = atomicAdd(&cursor[idx[p]], 1);
+    pair_of[place] = p;
+    place_of[p] = place;
+  }
 }
 
 // ----------------------------------------------------------------------------- the products
@@ -203,11 +210,10 @@ moe_gate_up_kernel(const T* __restrict__ h, int ldh, const T* __restrict__ wgu, 
   }
 }
 
-// y[pair, n] = sum_k act[place, k] Wd[e][n, k];  wd: [E, D, F];  y float, indexed by pair.
+// y[place, n] = sum_k act[place, k] Wd[e][n, k];  wd: [E, D, F];  y float, in the order of the sorted pairs.
 template <typename T>
 __global__ void __launch_bounds__(256)
-moe_down_kernel(const T* __restrict__ act, const T* __restrict__ wd, const int* __restrict__ pair_of,
-                const int* __restrict__ tile_expert, const int* __restrict__ tile_begin,
+moe_down_kernel(const T* __restrict__ act, const T* __restrict__ wd, const int* __restrict__ tile_expert, const int* __restrict__ tile_begin,
                 const int* __restrict__ tile_rows, const int* __restrict__ num_tiles, float* __restrict__ y,
                 int F, int D) {
   const int tile = blockIdx.y;
@@ -249,24 +255,25 @@ moe_down_kernel(const T* __restrict__ act, const T* __restrict__ wd, const int* 
   for (int i = 0; i < 4; ++i) {
     const int m = ty * 4 + i;
     if (m >= mrows) continue;
-    const size_t pair = pair_of[begin + m];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int gn = n0 + tx * 4 + j;
-      if (gn < D) y[pair * D + gn] = acc[i][j];
+      if (gn < D) y[size_t(begin + m) * D + gn] = acc[i][j];
     }
   }
 }
 
-// out[row, i] = sum_k wt[row, k] * y[row * top + k, i]  (+ gate[row] * shared[row, i])
+// out[row, i] = sum_k wt[row, k] * y[place_of[row * top + k], i]  (+ gate[row] * shared[row, i]),
+// the choices added in the order of k.
 template <typename T>
 __global__ void __launch_bounds__(256)
-moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ wt, int top, const float* __restrict__ shared_y,
-                   const float* __restrict__ gate, float* __restrict__ out, int D) {
+moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place_of, const float* __restrict__ wt, int top,
+                   const float* __restrict__ shared_y, const float* __restrict__ gate, float* __restrict__ out, int D) {
   const int row = blockIdx.x;
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
     float acc = 0.f;
-    for (int k = 0; k < top; ++k) acc = fmaf(wt[size_t(row) * top + k], y[(size_t(row) * top + k) * D + i], acc);
+    for (int k = 0; k < top; ++k)
+      acc = fmaf(wt[size_t(row) * top + k], y[size_t(place_of[size_t(row) * top + k]) * D + i], acc);
     if (shared_y) acc += (gate ? gate[row] : 1.f) * shared_y[size_t(row) * D + i];
     out[size_t(row) * D + i] = acc;
   }
@@ -290,30 +297,47 @@ int launch_moe_route(const void* h, int ldh, const void* wr, int w_f32, int rows
   return KVCM_LAUNCH_RESULT();
 }
 
+// The scratch of a step's routing, in ints: offsets[E + 1] | num_tiles[1] | pair_of[pairs] |
+// place_of[pairs] | tile_expert, tile_begin, tile_rows [pairs / tile_m + E each].
+struct MoeWork {
+  int *offsets, *num_tiles, *pair_of, *place_of, *tile_expert, *tile_begin, *tile_rows;
+  int max_tiles;
+};
+inline MoeWork moe_work(int* work, int pairs, int E, int tile_m) {
+  MoeWork w;
+  w.max_tiles = pairs / tile_m + E;
+  w.offsets = work;
+  w.num_tiles = work + E + 1;
+  w.pair_of = w.num_tiles + 1;
+  w.place_of = w.pair_of + pairs;
+  w.tile_expert = w.place_of + pairs;
+  w.tile_begin = w.tile_expert + w.max_tiles;
+  w.tile_rows = w.tile_begin + w.max_tiles;
+  return w;
+}
+
+int launch_moe_sort(const int* idx, int pairs, int E, int tile_m, int* work, cudaStream_t s) {
+  if (size_t(2 * E) * sizeof(int) > 48 * 1024 || pairs / tile_m + E > 65535) return KVCM_ERR_UNSUPPORTED;
+  const MoeWork w = moe_work(work, pairs, E, tile_m);
+  moe_sort_kernel<<<1, 1024, size_t(2 * E) * sizeof(int), s>>>(idx, pairs, E, tile_m, w.offsets, w.pair_of, w.place_of,
+                                                               w.tile_expert, w.tile_begin, w.tile_rows, w.num_tiles);
+  return KVCM_LAUNCH_RESULT();
+}
+
 template <typename T>
 int launch_moe_experts(const void* h, int ldh, const void* wgu, const void* wd, const int* idx, int rows, int top, int E,
                        int F, int D, int* work, void* act, float* y, cudaStream_t s) {
   if (rows == 0) return 0;
   const int pairs = rows * top;
-  const int max_tiles = pairs / MOE_TM + E;
-  if (max_tiles > 65535 || size_t(2 * E) * sizeof(int) > 48 * 1024) return KVCM_ERR_UNSUPPORTED;
-  // work: offsets[E + 1] | num_tiles[1] | pair_of[pairs] | tile_expert, tile_begin, tile_rows [max_tiles each]
-  int* offsets = work;
-  int* num_tiles = work + E + 1;
-  int* pair_of = num_tiles + 1;
-  int* tile_expert = pair_of + pairs;
-  int* tile_begin = tile_expert + max_tiles;
-  int* tile_rows = tile_begin + max_tiles;
-  moe_sort_kernel<<<1, 1024, size_t(2 * E) * sizeof(int), s>>>(idx, pairs, E, offsets, pair_of, tile_expert, tile_begin,
-                                                               tile_rows, num_tiles);
-  int rc = KVCM_LAUNCH_RESULT();
+  int rc = launch_moe_sort(idx, pairs, E, MOE_TM, work, s);
   if (rc) return rc;
-  moe_gate_up_kernel<T><<<dim3((F + MOE_TN - 1) / MOE_TN, max_tiles), 256, 0, s>>>(
-      (const T*)h, ldh, (const T*)wgu, pair_of, top, tile_expert, tile_begin, tile_rows, num_tiles, (T*)act, F, D);
+  const MoeWork w = moe_work(work, pairs, E, MOE_TM);
+  moe_gate_up_kernel<T><<<dim3((F + MOE_TN - 1) / MOE_TN, w.max_tiles), 256, 0, s>>>(
+      (const T*)h, ldh, (const T*)wgu, w.pair_of, top, w.tile_expert, w.tile_begin, w.tile_rows, w.num_tiles, (T*)act, F, D);
   rc = KVCM_LAUNCH_RESULT();
   if (rc) return rc;
-  moe_down_kernel<T><<<dim3((D + MOE_TN - 1) / MOE_TN, max_tiles), 256, 0, s>>>(
-      (const T*)act, (const T*)wd, pair_of, tile_expert, tile_begin, tile_rows, num_tiles, y, F, D);
+  moe_down_kernel<T><<<dim3((D + MOE_TN - 1) / MOE_TN, w.max_tiles), 256, 0, s>>>(
+      (const T*)act, (const T*)wd, w.tile_expert, w.tile_begin, w.tile_rows, w.num_tiles, y, F, D);
   return KVCM_LAUNCH_RESULT();
 }
 
@@ -321,10 +345,29 @@ int launch_moe_experts(const void* h, int ldh, const void* wgu, const void* wd, 
 
 using namespace kvcm;
 
-// Ints of scratch that kvcm_moe_experts_* needs for `rows` rows.
+// Ints of scratch that the experts' products need for `rows` rows (enough for tiles of 64 and of 128).
 KVCM_API long long kvcm_moe_work_ints(int rows, int top, int E) {
   const long long pairs = (long long)rows * top;
-  return (E + 2) + pairs + 3 * (pairs / MOE_TM + E);
+  return (E + 2) + 2 * pairs + 3 * (pairs / MOE_TM + E);
+}
+
+// The tensor-core form of the experts' products (csrc/cuda/moe_tcgen05.cu), after a sort into tiles of 128.
+extern "C" int kvcm_moe_experts_tcgen05_bf16(const void* h, int ldh, const void* wgu, const void* wd, const int* pair_of,
+                                             const int* tile_expert, const int* tile_begin, const int* tile_rows,
+                                             const int* num_tiles, int pairs, int top, int E, int F, int D, void* xs,
+                                             void* act, float* y, void* stream);
+
+// y in the order of the sorted pairs; `xs` [pairs, D] bf16 scratch.  Tensor-core products.
+KVCM_API int kvcm_moe_experts_tc_bf16(const void* h, int ldh, const void* wgu, const void* wd, const int* idx, int rows,
+                                      int top, int E, int F, int D, int* work, void* xs, void* act, float* y,
+                                      void* stream) {
+  if (rows == 0) return 0;
+  const int pairs = rows * top;
+  int rc = launch_moe_sort(idx, pairs, E, 128, work, (cudaStream_t)stream);
+  if (rc) return rc;
+  const MoeWork w = moe_work(work, pairs, E, 128);
+  return kvcm_moe_experts_tcgen05_bf16(h, ldh, wgu, wd, w.pair_of, w.tile_expert, w.tile_begin, w.tile_rows, w.num_tiles,
+                                       pairs, top, E, F, D, xs, act, y, stream);
 }
 
 #define KVCM_MOE(SUFFIX, T)                                                                                          \
@@ -343,9 +386,11 @@ KVCM_API long long kvcm_moe_work_ints(int rows, int top, int E) {
 KVCM_MOE(f32, float)
 KVCM_MOE(bf16, bf16)
 
-KVCM_API int kvcm_moe_combine(const float* y, const float* wt, int top, const float* shared_y, const float* gate,
-                              float* out, int rows, int D, void* stream) {
+// `work` is the scratch the experts' products were given (it holds the place of every pair).
+KVCM_API int kvcm_moe_combine(const float* y, const int* work, const float* wt, int top, int E, const float* shared_y,
+                              const float* gate, float* out, int rows, int D, void* stream) {
   if (rows == 0) return 0;
-  moe_combine_kernel<float><<<rows, 256, 0, (cudaStream_t)stream>>>(y, wt, top, shared_y, gate, out, D);
+  const int* place_of = work + E + 2 + rows * top;
+  moe_combine_kernel<float><<<rows, 256, 0, (cudaStream_t)stream>>>(y, place_of, wt, top, shared_y, gate, out, D);
   return KVCM_LAUNCH_RESULT();
 }

@@ -17,7 +17,7 @@
 namespace kvcm {
 
 constexpr int kSampleThreads = 1024;
-constexpr int kStatusWords = 5;
+constexpr int kStatusWords = 6;
 
 // The error words of the kernel families whose waits are bounded (0 = healthy).  The sampling
 // kernels read them at the end of a step and write the first that is set beside the sampled
@@ -185,6 +185,7 @@ const int* kvcm_tcgen05_error_address(void);
 const int* kvcm_gemm_tcgen05_pair_error_address(void);
 const int* kvcm_gemm_tcgen05_splitk_error_address(void);
 const int* kvcm_attention_tcgen05_error_address(void);
+const int* kvcm_moe_tcgen05_error_address(void);
 }
 
 // The families in the order of the status index (1-based in status[0]): streaming product,
@@ -196,6 +197,7 @@ static StatusWords status_words() {
   sw.word[2] = kvcm_gemm_tcgen05_pair_error_address();
   sw.word[3] = kvcm_gemm_tcgen05_splitk_error_address();
   sw.word[4] = kvcm_attention_tcgen05_error_address();
+  sw.word[5] = kvcm_moe_tcgen05_error_address();
   return sw;
 }
 

@@ -307,7 +307,8 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
 
 # Kernel families whose bounded waits report through an error word, in the order of the status
 # index that the sampling kernels write (csrc/cuda/sampling.cu: status_words).
-STATUS_FAMILIES = ("gemm_stream", "gemm_tcgen05", "gemm_tcgen05_pair", "gemm_tcgen05_splitk", "attention_tcgen05")
+STATUS_FAMILIES = ("gemm_stream", "gemm_tcgen05", "gemm_tcgen05_pair", "gemm_tcgen05_splitk", "attention_tcgen05",
+                   "moe_tcgen05")
 
 
 def describe_status(first: int, word: int) -> str:
@@ -329,14 +330,15 @@ def raise_on_status(first: int, word: int) -> None:
 
 def clear_errors() -> None:
     """Reads and clears every family's error word (synchronises with the device)."""
-    for fn in (stream_error, tcgen05_error, pair_error, splitk_error, attention_tcgen05_error):
+    for fn in (stream_error, tcgen05_error, pair_error, splitk_error, attention_tcgen05_error, moe_tcgen05_error):
         fn()
 
 
 def check_errors() -> None:
     """Host-side read of every family's error word (synchronises); raises if one is set.  For paths
     that synchronise anyway (scoring, replay); generation reads the status pair beside its tokens."""
-    for i, fn in enumerate((stream_error, tcgen05_error, pair_error, splitk_error, attention_tcgen05_error)):
+    for i, fn in enumerate((stream_error, tcgen05_error, pair_error, splitk_error, attention_tcgen05_error,
+                            moe_tcgen05_error)):
         word = fn()
         if word:
             clear_errors()
@@ -1029,11 +1031,23 @@ def moe_work_ints(rows: int, top: int, experts: int) -> int:
     return int(_lib().kvcm_moe_work_ints(int(rows), int(top), int(experts)))
 
 
+def moe_tcgen05_supported(expert_ff: int, hidden: int) -> bool:
+    return bool(_lib().kvcm_moe_tcgen05_supports(int(expert_ff), int(hidden)))
+
+
+def moe_tcgen05_error() -> int:
+    """Error word of the experts' tensor-core products: 0, or (code << 16 | block) of a bounded wait
+    that ran out.  Reading clears it.  Synchronises the device."""
+    return int(_lib().kvcm_moe_tcgen05_error())
+
+
 def moe_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, idx: torch.Tensor,
-                work: torch.Tensor, act: torch.Tensor, y: torch.Tensor) -> None:
-    """y[t * top + k] = expert idx[t, k] applied to h[t] (float32 [T * top, D]); w_gate_up [E, 2F, D]
-    (gate rows before up rows), w_down [E, D, F]; act [T * top, F] and work int32 are scratch."""
-    _cuda(h, w_gate_up, w_down, idx, work, act, y)
+                work: torch.Tensor, act: torch.Tensor, y: torch.Tensor, xs: Optional[torch.Tensor] = None) -> None:
+    """y[place of (t, k)] = expert idx[t, k] applied to h[t] (float32 [T * top, D], in the order of the
+    pairs sorted by expert; ``work`` keeps every pair's place for ``moe_combine``); w_gate_up
+    [E, 2F, D] (gate rows before up rows), w_down [E, D, F]; act [T * top, F] and work int32 are
+    scratch.  With ``xs`` (bfloat16 [T * top, D] scratch) the products run on the tensor cores."""
+    _cuda(h, w_gate_up, w_down, idx, work, act, y, xs)
     T, D = h.shape
     top = idx.shape[1]
     E, F2, _ = w_gate_up.shape
@@ -1043,20 +1057,30 @@ def moe_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
     _need(h.stride(1) == 1 and act.is_contiguous() and act.shape == (T * top, F) and y.dtype == torch.float32
           and y.is_contiguous() and y.shape == (T * top, D), "moe_experts: buffers")
     _need(work.dtype == _I32 and work.numel() >= moe_work_ints(T, top, E), "moe_experts: work too small")
+    global _launches
+    if xs is not None:
+        _need(h.dtype == torch.bfloat16 and xs.dtype == torch.bfloat16 and xs.is_contiguous() and xs.shape == (T * top, D),
+              "moe_experts: the tensor-core form takes bfloat16 rows and a [pairs, width] scratch")
+        _check(_lib().kvcm_moe_experts_tc_bf16(_p(h), h.stride(0), _p(w_gate_up), _p(w_down), _p(idx), T, top, E, F, D,
+                                               _p(work), _p(xs), _p(act), _p(y), _stream()),
+               "moe_experts_tcgen05", f"(experts={E}, ff={F})")
+        _launches += 3                      # sort, gather, gate/up, down
+        return
     fn = getattr(_lib(), "kvcm_moe_experts_" + _suffix(h))
     _check(fn(_p(h), h.stride(0), _p(w_gate_up), _p(w_down), _p(idx), T, top, E, F, D, _p(work), _p(act), _p(y), _stream()),
            "moe_experts", f"(experts={E}, ff={F})")
-    global _launches
     _launches += 2                          # sort, gate/up, down
 
 
-def moe_combine(y: torch.Tensor, wt: torch.Tensor, shared_y: Optional[torch.Tensor], gate: Optional[torch.Tensor],
-                out: torch.Tensor) -> None:
-    """out[t] = sum_k wt[t, k] * y[t * top + k] + gate[t] * shared_y[t]; all float32."""
-    _cuda(y, wt, shared_y, gate, out)
+def moe_combine(y: torch.Tensor, work: torch.Tensor, wt: torch.Tensor, experts: int, shared_y: Optional[torch.Tensor],
+                gate: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out[t] = sum_k wt[t, k] * y[place of (t, k)] + gate[t] * shared_y[t]; all float32; ``work`` is the
+    scratch that ``moe_experts`` filled."""
+    _cuda(y, work, wt, shared_y, gate, out)
     T, D = out.shape
     top = wt.shape[1]
     _need(all(t is None or (t.dtype == torch.float32 and t.is_contiguous()) for t in (y, wt, shared_y, gate, out)),
           "moe_combine: float32")
-    _need(y.shape == (T * top, D) and (shared_y is None or shared_y.shape == (T, D)), "moe_combine: shapes")
-    _check(_lib().kvcm_moe_combine(_p(y), _p(wt), top, _p(shared_y), _p(gate), _p(out), T, D, _stream()), "moe_combine")
+    _need(y.shape == (T * top, D) and (shared_y is None or shared_y.shape == (T, D)) and work.dtype == _I32, "moe_combine: shapes")
+    _check(_lib().kvcm_moe_combine(_p(y), _p(work), _p(wt), top, int(experts), _p(shared_y), _p(gate), _p(out), T, D,
+                                   _stream()), "moe_combine")

@@ -60,8 +60,12 @@ class RoutedExperts(FeedForward):
         work = torch.empty((K.moe_work_ints(M, top, self.experts),), dtype=torch.int32, device=dev)
         act = torch.empty((M * top, self.expert_ff), dtype=h.dtype, device=dev)
         y = torch.empty((M * top, D), dtype=torch.float32, device=dev)
-        K.moe_experts(h, self._wgu, self._wd, idx, work, act, y)
+        xs = None
+        if (h.dtype == torch.bfloat16 and ctx.options.get("gemm", "auto") != "plain"
+                and K.moe_tcgen05_supported(self.expert_ff, D) and h.stride(0) % 8 == 0):
+            xs = torch.empty((M * top, D), dtype=h.dtype, device=dev)        # tensor-core products
+        K.moe_experts(h, self._wgu, self._wd, idx, work, act, y, xs)
         shared_y = self.shared.forward(h, ctx, out_dtype=torch.float32) if self.shared is not None else None
         out = torch.empty((M, D), dtype=torch.float32, device=dev)
-        K.moe_combine(y, wt, shared_y, gate, out)
+        K.moe_combine(y, work, wt, self.experts, shared_y, gate, out)
         return out

@@ -375,3 +375,43 @@ def test_trace_tool_on_a_model_folder(tmp_path, folders, oracle):
     close(torch.from_numpy(out[1][:1]), ref[[71]], dtype, "trace tool step 1")
     close(torch.from_numpy(out[1][1:]), oracle(name, dtype, 1)[[63]], dtype, "trace tool step 1, second request")
     close(torch.from_numpy(out[2]), ref[[len(toks) - 1]], dtype, "trace tool step 2")
+
+
+@pytest.mark.parametrize("T,E,top,F,D", [(300, 8, 2, 192, 320), (5, 16, 4, 72, 136), (1, 3, 3, 264, 64), (700, 4, 1, 40, 520)])
+def test_expert_products_on_tensor_cores_against_float64(T, E, top, F, D):
+    """The experts' products alone: bfloat16 rows through the tensor-core kernels and through the
+    plain kernels, both against float64 on the same bfloat16 values.  Experts that get no row, tiles
+    of fewer than 128 pairs beside full ones, sizes that are no multiple of the tile."""
+    from kvcm.kernels import library as K
+    g = torch.Generator().manual_seed(T + E)
+    h = (torch.randn(T, D, generator=g) * 0.5).to(torch.bfloat16).cuda()
+    wgu = (torch.randn(E, 2 * F, D, generator=g) * D ** -0.5).to(torch.bfloat16).cuda()
+    wd = (torch.randn(E, D, F, generator=g) * F ** -0.5).to(torch.bfloat16).cuda()
+    idx = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(T)]).to(torch.int32)
+    if E > 3:
+        idx[idx == 1] = 0 if top == 1 else idx[idx == 1]          # (top 1: expert 1 gets no row at all)
+    idx = idx.cuda()
+    wt = torch.rand(T, top, generator=g).cuda()
+    hd, gud, dd = h.double().cpu(), wgu.double().cpu(), wd.double().cpu()
+    ref = torch.zeros(T, D, dtype=torch.float64)
+    for t in range(T):
+        for k in range(top):
+            e = int(idx[t, k])
+            a = P.silu(gud[e, :F] @ hd[t]) * (gud[e, F:] @ hd[t])
+            ref[t] += wt[t, k].double().cpu() * (dd[e] @ a)
+    outs = []
+    for tensor_cores in (True, False):
+        work = torch.empty(K.moe_work_ints(T, top, E), dtype=torch.int32, device="cuda")
+        act = torch.empty(T * top, F, dtype=torch.bfloat16, device="cuda")
+        y = torch.empty(T * top, D, dtype=torch.float32, device="cuda")
+        xs = torch.empty(T * top, D, dtype=torch.bfloat16, device="cuda") if tensor_cores else None
+        out = torch.empty(T, D, dtype=torch.float32, device="cuda")
+        K.moe_experts(h, wgu, wd, idx, work, act, y, xs)
+        K.moe_combine(y, work, wt, E, None, None, out)
+        torch.cuda.synchronize()
+        K.check_errors()
+        outs.append(out.cpu().double())
+        # what remains is the rounding of act to bfloat16 (unit roundoff 2^-8) in a sum over F whose terms have
+        # heavy tails; the largest of some 10^5 such errors stays below 4 % of the spread, a fault is of its order
+        assert (outs[-1] - ref).abs().max().item() <= 0.04 * ref.std().item(), ("tensor cores" if tensor_cores else "plain")
+    assert (outs[0] - outs[1]).abs().max().item() <= 0.04 * ref.std().item()

@@ -18,4 +18,4 @@ def test_status_pair_names_family_code_and_block(monkeypatch):
     with pytest.raises(K.KernelError, match=r"attention_tcgen05: .*code 7, block 3"):
         K.raise_on_status(5, (7 << 16) | 3)
     assert "family 9" in K.describe_status(9, 1 << 16)
-    assert len(K.STATUS_FAMILIES) == 5
+    assert len(K.STATUS_FAMILIES) == 6
