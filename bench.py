@@ -228,6 +228,173 @@ def prefill_run(spec, ec, vocab, cfg, layers, reps=5):
     torch.cuda.empty_cache()
     return statistics.median(dev), gemm_flops + attn_flops, statistics.median(wall)
 
+# ------------------------------------------------------------------------------------------------
+# --compare tolanex: the Tolanex design beside the Llama decoder at equal width, depth and active
+# feed-forward size (random bfloat16 weights): prefill of one 2,048-token prompt and decode steps
+# of 8 requests at a context of about 1,024, device time from CUDA events, and the device time of
+# every kernel family of one eager step of each kind with what that family has to compute or move.
+
+COMPARE_SIZES = {
+    # width, layers, heads x head size, latent rank, experts / top / expert ff / groups, shared ff
+    "w2048": dict(width=2048, layers=4, heads=16, dim=128, rank=128, experts=32, top=4, ff=512, groups=(4, 2), shared=1024,
+                  kv_heads=4),
+    "w4096": dict(width=4096, layers=2, heads=32, dim=128, rank=256, experts=64, top=6, ff=1024, groups=(8, 4), shared=2048,
+                  kv_heads=8),
+}
+COMPARE_VOCAB = 32000
+
+
+def compare_configs(z):
+    """(Tolanex config, Llama config) of one size.  Tolanex layers alternate delta / latent attention;
+    every second latent layer reads the pages of the one before it."""
+    from kvcm.config import LlamaConfig, config_from_dict
+    D, H, d = z["width"], z["heads"], z["dim"]
+    mlp = {"kind": "moe", "expert": {"ff": z["ff"]}, "shared": {"ff": z["shared"]},
+           "router": {"experts": z["experts"], "top": z["top"], "scale": 1.0,
+                      "groups": {"count": z["groups"][0], "keep": z["groups"][1]}}}
+    layers, last_latent, latents = [], None, 0
+    for i in range(z["layers"]):
+        if i % 2 == 0:
+            layers.append({"type": "delta", "mixer": {"heads": H, "kv_heads": H // 2, "dim": d, "vdim": d, "conv": 4}, "mlp": mlp})
+        else:
+            m = {"heads": H, "dim": d, "vdim": d, "kv_rank": z["rank"], "scale": d ** -0.5}
+            if latents % 2 == 1:
+                m["kv_from"] = last_latent
+            else:
+                last_latent = i
+            latents += 1
+            layers.append({"type": "latent_attention", "mixer": m, "mlp": mlp})
+    tol = config_from_dict({"architecture": "Tolanex", "vocab": COMPARE_VOCAB, "width": D, "max_positions": 4096,
+                            "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+                            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 127, "mul_cur": 17}}, "layers": layers})
+    active_ff = z["top"] * z["ff"] + z["shared"]
+    lla = LlamaConfig(architecture="LlamaForCausalLM", vocab_size=COMPARE_VOCAB, hidden_size=D, intermediate_size=active_ff,
+                      num_hidden_layers=z["layers"], num_attention_heads=H, num_key_value_heads=z["kv_heads"], head_dim=d,
+                      max_position_embeddings=4096, rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=False)
+    return tol, lla
+
+
+def family_profile(spec, vocab, kind):
+    """Device ms per kernel family of ONE eager step: kind 'prefill' (one prompt of 2,048 tokens) or
+    'decode' (8 requests with 1,024 cached tokens, one token each)."""
+    import torch
+    from kvcm.engine.replay import ReplaySession
+    from kvcm.kernels import library as K
+    s = ReplaySession(spec, "bfloat16", 8 * 1088 + 2112, block_size=BLOCK_SIZE, max_live=9)
+    g = torch.Generator().manual_seed(5)
+    if kind == "prefill":
+        toks = torch.randint(3, vocab, (3, PREFILL_TOKENS), generator=g).tolist()
+        for i in range(2):
+            s.step([dict(id=f"w{i}", tokens=toks[i], want=[PREFILL_TOKENS - 1])], end=[f"w{i}"])
+        torch.cuda.synchronize()
+        K.profile_start()
+        s.step([dict(id="p", tokens=toks[2], want=[PREFILL_TOKENS - 1])], end=["p"])
+        return K.profile_stop()
+    toks = torch.randint(3, vocab, (8, 1024 + 3), generator=g).tolist()
+    for i in range(8):
+        s.step([dict(id=i, tokens=toks[i][:1024], want=[])])
+    for k in range(2):
+        s.step([dict(id=i, tokens=[toks[i][1024 + k]], want=[0]) for i in range(8)])
+    torch.cuda.synchronize()
+    K.profile_start()
+    s.step([dict(id=i, tokens=[toks[i][1026]], want=[0]) for i in range(8)])
+    return K.profile_stop()
+
+
+def tolanex_work(z, T, ctx, decode):
+    """What the families of one Tolanex step have to do at least: flops, or bytes they must move."""
+    D, H, d, R, E, top, F = z["width"], z["heads"], z["dim"], z["rank"], z["experts"], z["top"], z["ff"]
+    n_delta, n_latent = (z["layers"] + 1) // 2, z["layers"] // 2
+    hit = min(E, T * top)                                        # experts that get a row, at most
+    return {
+        "moe_experts_tcgen05": dict(flops=2.0 * T * top * 3 * F * D * z["layers"],
+                                    bytes=2.0 * hit * 3 * F * D * z["layers"] if decode else None),
+        "delta_scan": dict(flops=6.0 * T * H * d * d * n_delta,                      # two dot products and one update a token
+                           bytes=(8.0 if decode else 0.0) * T * H * d * d * n_delta if decode else None),   # state read + written
+        "attention": dict(flops=4.0 * R * H * (T * ctx if decode else T * (T + 1) / 2) * n_latent,
+                          bytes=2.0 * T * ctx * R * n_latent if decode else None),
+    }
+
+
+def llama_work(z, T, ctx, decode):
+    D, H, d = z["width"], z["heads"], z["dim"]
+    I = z["top"] * z["ff"] + z["shared"]
+    L = z["layers"]
+    return {
+        "feed_forward": dict(flops=2.0 * T * 3 * I * D * L, bytes=2.0 * 3 * I * D * L if decode else None),
+        "attention": dict(flops=4.0 * d * H * (T * ctx if decode else T * (T + 1) / 2) * L,
+                          bytes=2.0 * 2 * T * ctx * z["kv_heads"] * d * L if decode else None),
+    }
+
+
+def compare_main(args) -> int:
+    import torch
+    from kvcm.config import EngineConfig, KVManagerConfig, SchedulerConfig
+    from kvcm.engine import model_from_tensors
+    from kvcm.weights import random_tensors
+    pk = peaks()
+    out = {"compare": "tolanex beside llama at equal width, depth and active feed-forward size", "dtype": "bf16",
+           "data": "synthetic: random weights, uniform random token ids", "peaks": pk, "sizes": {}}
+    steps, warmup = min(args.steps, 200), max(args.warmup, 3)
+    for name, z in COMPARE_SIZES.items():
+        if args.size not in ("all", name):
+            continue
+        res = {}
+        for arch, cfg in zip(("tolanex", "llama"), compare_configs(z)):
+            tensors = dict(random_tensors(cfg, 0, torch.bfloat16, device="cuda:0"))
+            spec = model_from_tensors(cfg, tensors, "bfloat16", "cuda:0")
+            del tensors
+            max_len = 1280 + warmup + steps + 64
+            ec = EngineConfig(kv=KVManagerConfig(num_blocks=8 * (max_len // BLOCK_SIZE + 2) + 160, block_size=BLOCK_SIZE,
+                                                 max_seq_len=max(max_len, PREFILL_TOKENS + 16), watermark_blocks=0),
+                              sched=SchedulerConfig(max_num_seqs=8, max_batched_tokens=4096), dtype="bfloat16")
+            dec = decode_run(spec, ec, COMPARE_VOCAB, 8, steps, warmup, 1280 - warmup - steps // 2)   # contexts of one graph bucket
+            pre = prefill_times(spec, ec, COMPARE_VOCAB)
+            fam = {k: {kk: {"calls": c, "ms": round(ms, 4)} for kk, (c, ms) in family_profile(spec, COMPARE_VOCAB, k).items()}
+                   for k in ("prefill", "decode")}
+            work = {"prefill": (tolanex_work if arch == "tolanex" else llama_work)(z, PREFILL_TOKENS, PREFILL_TOKENS, False),
+                    "decode": (tolanex_work if arch == "tolanex" else llama_work)(z, 8, 1024, True)}
+            res[arch] = {"decode_tokens_per_s": round(8 * steps * 1e3 / dec["dev_ms"], 1),
+                         "decode_ms_per_step": round(dec["dev_ms"] / steps, 4),
+                         "decode_e2e_tokens_per_s": round(8 * steps * 1e3 / dec["wall_ms"], 1),
+                         "decode_graph_steps": dec["graph_steps"], "gpu_launches": int(dec["launches"]),
+                         "prefill_tokens_per_s": round(PREFILL_TOKENS * 1e3 / pre[0], 1), "prefill_ms": round(pre[0], 3),
+                         "prefill_e2e_ms": round(pre[1], 3), "families": fam, "work": work}
+            del spec
+            torch.cuda.empty_cache()
+        out["sizes"][name] = dict(z, **res)
+    print(json.dumps(out))
+    return 0
+
+
+def prefill_times(spec, ec, vocab, reps=3):
+    """(device ms, end-to-end ms) of one prompt of PREFILL_TOKENS tokens in one step through the engine."""
+    import torch
+    from kvcm.engine.engine import DeviceTimer, Engine
+    eng = Engine(spec, ec)
+    g = torch.Generator().manual_seed(2)
+    dev, wall = [], []
+    for r in range(reps + 2):
+        toks = torch.randint(3, vocab, (PREFILL_TOKENS,), generator=g).tolist()
+        timer = DeviceTimer()
+        eng.device_timer = timer
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        eng.add_request(toks, max_new_tokens=1)
+        info = eng.step()
+        t1 = time.perf_counter()
+        assert info.prefill_tokens == PREFILL_TOKENS and info.sampled == 1, info
+        eng.take_finished()
+        ms = timer.total_ms()
+        eng.device_timer = None
+        if r >= 2:
+            dev.append(ms)
+            wall.append((t1 - t0) * 1e3)
+    del eng
+    torch.cuda.empty_cache()
+    return statistics.median(dev), statistics.median(wall)
+
+
 def reference_main(args) -> int:
     """The same metric and shape through the unmodified reference (fp16, its own kvbench)."""
     sys.path.insert(0, os.path.join(ROOT, "baseline"))
@@ -326,10 +493,16 @@ def main() -> int:
                          "'native' this engine's kernels only, 'library' the library wherever it can stand")
     ap.add_argument("--only", default="all", choices=["all", "prefill"],
                     help="'prefill': run only the 2,048-token prefill step and print its numbers (for profiling)")
+    ap.add_argument("--compare", default="", choices=["", "tolanex"],
+                    help="'tolanex': instead of the default workload, prefill and decode of the Tolanex design beside "
+                         "the Llama decoder at equal sizes, with device time per kernel family")
+    ap.add_argument("--size", default="all", choices=["all"] + sorted(COMPARE_SIZES), help="with --compare: one size only")
     args = ap.parse_args()
 
     if args.impl == "reference":
         return reference_main(args)
+    if args.compare:
+        return compare_main(args)
     if args.gpus != 1:
         print(f"bench.py: this engine is single-GPU by design; --gpus {args.gpus} is not supported "
               f"(run with --gpus 1)")

@@ -15,7 +15,9 @@
 // The columns of S are independent of each other, so the recurrence is spread over
 // (request, head, 32 columns) blocks; inside a block four lanes share a column (rows r, r+4, ...
 // each) and add their partial dot products by shuffles.  The same kernel serves portions of
-// prompts and single decoded tokens: it walks the request's rows of the step in order.
+// prompts and single decoded tokens: it walks the request's rows of the step in order.  The
+// recurrence is one dependent chain per column (dot product, step, update) whose length per token
+// is what bounds a long portion of ONE request; requests and heads run side by side.
 #include "common.cuh"
 
 namespace kvcm {
@@ -99,21 +101,31 @@ delta_prepare_kernel(float* __restrict__ qkv, int channels, float* __restrict__ 
 }
 
 // ------------------------------------------------------------------------------ the recurrence
-constexpr int DR_TOKENS = 16;    // tokens staged in shared memory at a time
 constexpr int DR_COLS = 32;      // columns of S per block
 constexpr int DR_LANES = 4;      // lanes that share a column
 
-template <int NI>                // rows of S per thread: dk <= 4 * NI
+// 4 bytes from global to shared memory without passing through registers; `ok` false writes zero.
+__device__ __forceinline__ void dr_copy4(float* dst, const float* src, bool ok) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
+  const int bytes = ok ? 4 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+
+// NI: rows of S per thread (dk <= 4 * NI).  TT tokens are staged in shared memory at a time, in two
+// buffers: while one tile of tokens is worked through, the next is on its way (cp.async).
+template <int NI, int TT>
 __global__ void __launch_bounds__(DR_COLS * DR_LANES)
 delta_scan_kernel(const float* __restrict__ qkv, int channels, const float* __restrict__ bg,
                   float* __restrict__ state, long long state_stride, const int* __restrict__ seq_q_start,
                   const int* __restrict__ seq_q_len, const int* __restrict__ seq_state_slot,
                   float* __restrict__ out, int heads, int qk_heads, int dk, int dv) {
   constexpr int DKP = DR_LANES * NI;
-  __shared__ float qs[DR_TOKENS][DKP];
-  __shared__ float ks[DR_TOKENS][DKP];
-  __shared__ float vs[DR_TOKENS][DR_COLS];
-  __shared__ float bs[DR_TOKENS], gs[DR_TOKENS];
+  constexpr int NIP = NI + 4;      // a lane's NI values lie together (element i = r + 4 m at [i % 4][i / 4]); the pad
+                                   // puts the four lanes' 16-byte loads on different banks
+  __shared__ __align__(16) float qs[2][TT][DR_LANES][NIP];
+  __shared__ __align__(16) float ks[2][TT][DR_LANES][NIP];
+  __shared__ float vs[2][TT][DR_COLS];
+  __shared__ float bs[2][TT], gs[2][TT];
   const int s = blockIdx.z, head = blockIdx.y;
   const int slot = seq_state_slot[s];
   if (slot < 0) return;
@@ -133,41 +145,66 @@ delta_scan_kernel(const float* __restrict__ qkv, int channels, const float* __re
   }
   const size_t q_off = size_t(qk_head) * dk, k_off = size_t(qk_heads + qk_head) * dk;
   const size_t v_off = size_t(2 * qk_heads) * dk + size_t(head) * dv + size_t(blockIdx.x) * DR_COLS;
-  for (int t0 = 0; t0 < n; t0 += DR_TOKENS) {
-    const int nt = min(DR_TOKENS, n - t0);
-    __syncthreads();                                   // the previous tile has been consumed
-    for (int idx = threadIdx.x; idx < DR_TOKENS * DKP; idx += blockDim.x) {
+
+  auto stage = [&](int buf, int t0) {                   // asks for the tile of tokens t0 .. t0 + TT - 1
+    const int nt = min(TT, n - t0);
+    for (int idx = threadIdx.x; idx < TT * DKP; idx += blockDim.x) {
       const int t = idx / DKP, i = idx % DKP;
       const bool ok = t < nt && i < dk;
-      const float* src = qkv + size_t(q0 + t0 + t) * channels;
-      qs[t][i] = ok ? src[q_off + i] : 0.f;
-      ks[t][i] = ok ? src[k_off + i] : 0.f;
+      const float* src = qkv + (ok ? size_t(q0 + t0 + t) * channels : 0);
+      dr_copy4(&qs[buf][t][i % DR_LANES][i / DR_LANES], src + (ok ? q_off + i : 0), ok);
+      dr_copy4(&ks[buf][t][i % DR_LANES][i / DR_LANES], src + (ok ? k_off + i : 0), ok);
     }
-    for (int idx = threadIdx.x; idx < DR_TOKENS * DR_COLS; idx += blockDim.x) {
+    for (int idx = threadIdx.x; idx < TT * DR_COLS; idx += blockDim.x) {
       const int t = idx / DR_COLS, c = idx % DR_COLS;
       const bool ok = t < nt && blockIdx.x * DR_COLS + c < dv;
-      vs[t][c] = ok ? qkv[size_t(q0 + t0 + t) * channels + v_off + c] : 0.f;
+      dr_copy4(&vs[buf][t][c], qkv + (ok ? size_t(q0 + t0 + t) * channels + v_off + c : 0), ok);
     }
-    if (threadIdx.x < DR_TOKENS) {
+    if (threadIdx.x < TT) {
       const int t = threadIdx.x;
-      bs[t] = t < nt ? bg[size_t(q0 + t0 + t) * 2 * heads + head] : 0.f;
-      gs[t] = t < nt ? bg[size_t(q0 + t0 + t) * 2 * heads + heads + head] : 1.f;
+      const bool ok = t < nt;
+      dr_copy4(&bs[buf][t], bg + (ok ? size_t(q0 + t0 + t) * 2 * heads + head : 0), ok);
+      dr_copy4(&gs[buf][t], bg + (ok ? size_t(q0 + t0 + t) * 2 * heads + heads + head : 0), ok);
     }
-    __syncthreads();
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+
+  stage(0, 0);
+  for (int t0 = 0, buf = 0; t0 < n; t0 += TT, buf ^= 1) {
+    const int nt = min(TT, n - t0);
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();                                   // this tile has landed; the other buffer has been consumed
+    if (t0 + TT < n) stage(buf ^ 1, t0 + TT);
     for (int t = 0; t < nt; ++t) {
-      const float g = gs[t], beta = bs[t];
-      float p = 0.f;
+      const float g = gs[buf][t], beta = bs[buf][t];
+      float kt[NI], qt[NI];
+      if constexpr (NI % 4 == 0) {
 #pragma unroll
-      for (int m = 0; m < NI; ++m) p = fmaf(acc[m], ks[t][r + DR_LANES * m], p);
+        for (int m = 0; m < NI; m += 4) {
+          const float4 a = *reinterpret_cast<const float4*>(&ks[buf][t][r][m]);
+          const float4 b = *reinterpret_cast<const float4*>(&qs[buf][t][r][m]);
+          kt[m] = a.x; kt[m + 1] = a.y; kt[m + 2] = a.z; kt[m + 3] = a.w;
+          qt[m] = b.x; qt[m + 1] = b.y; qt[m + 2] = b.z; qt[m + 3] = b.w;
+        }
+      } else {
+#pragma unroll
+        for (int m = 0; m < NI; ++m) { kt[m] = ks[buf][t][r][m]; qt[m] = qs[buf][t][r][m]; }
+      }
+      // four partial sums each: the chain of dependent FMAs is a quarter as long
+      float p4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int m = 0; m < NI; ++m) p4[m & 3] = fmaf(acc[m], kt[m], p4[m & 3]);
+      float p = (p4[0] + p4[1]) + (p4[2] + p4[3]);
       p += __shfl_xor_sync(0xffffffffu, p, 8);
       p += __shfl_xor_sync(0xffffffffu, p, 16);
-      const float u = beta * (vs[t][col_local] - g * p);
-      float o = 0.f;
+      const float u = beta * (vs[buf][t][col_local] - g * p);
+      float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int m = 0; m < NI; ++m) {
-        acc[m] = fmaf(ks[t][r + DR_LANES * m], u, g * acc[m]);
-        o = fmaf(acc[m], qs[t][r + DR_LANES * m], o);
+        acc[m] = fmaf(kt[m], u, g * acc[m]);
+        o4[m & 3] = fmaf(acc[m], qt[m], o4[m & 3]);
       }
+      float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
       o += __shfl_xor_sync(0xffffffffu, o, 8);
       o += __shfl_xor_sync(0xffffffffu, o, 16);
       if (r == 0 && col_ok) out[size_t(q0 + t0 + t) * heads * dv + size_t(head) * dv + col] = o;
@@ -253,16 +290,16 @@ KVCM_API int kvcm_delta_scan(const float* qkv, int channels, const float* bg, fl
   if (dk < 1 || dk > DR_LANES * 64 || qk_heads < 1 || heads % qk_heads) return KVCM_ERR_UNSUPPORTED;
   const dim3 grid((dv + DR_COLS - 1) / DR_COLS, heads, seqs), block(DR_COLS * DR_LANES);
   cudaStream_t s = (cudaStream_t)stream;
-#define KVCM_SCAN(NI)                                                                                              \
-  delta_scan_kernel<NI><<<grid, block, 0, s>>>(qkv, channels, bg, state, state_stride, seq_q_start, seq_q_len,     \
-                                               seq_state_slot, out, heads, qk_heads, dk, dv)
+#define KVCM_SCAN(NI, TT)                                                                                          \
+  delta_scan_kernel<NI, TT><<<grid, block, 0, s>>>(qkv, channels, bg, state, state_stride, seq_q_start, seq_q_len, \
+                                                   seq_state_slot, out, heads, qk_heads, dk, dv)
   const int need = (dk + DR_LANES - 1) / DR_LANES;
-  if (need <= 2) KVCM_SCAN(2);
-  else if (need <= 4) KVCM_SCAN(4);
-  else if (need <= 8) KVCM_SCAN(8);
-  else if (need <= 16) KVCM_SCAN(16);
-  else if (need <= 32) KVCM_SCAN(32);
-  else KVCM_SCAN(64);
+  if (need <= 2) KVCM_SCAN(2, 16);
+  else if (need <= 4) KVCM_SCAN(4, 16);
+  else if (need <= 8) KVCM_SCAN(8, 16);
+  else if (need <= 16) KVCM_SCAN(16, 16);
+  else if (need <= 32) KVCM_SCAN(32, 16);
+  else KVCM_SCAN(64, 8);
 #undef KVCM_SCAN
   return KVCM_LAUNCH_RESULT();
 }

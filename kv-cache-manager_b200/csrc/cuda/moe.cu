@@ -36,73 +36,126 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 }
 
 // ------------------------------------------------------------------------------------ route
-template <typename T, typename W>
-__global__ void __launch_bounds__(128)
+// One block of eight warps for RB rows: the rows of h are staged in shared memory as floats, the
+// warps share out the experts (each logit one warp's sum over the width, float FMAs, 16-byte loads
+// of the router's rows where they are aligned; a piece of the router's row is loaded once for all
+// RB rows), then warp w does the softmax and the choice of rows w, w + 8, ...  RB = 1 for steps of
+// few rows (more blocks), up to 8 for many (the router matrix is read once per block).
+constexpr int ROUTE_WARPS = 8;
+
+template <typename W> struct RouteVec;                     // elements of a 16-byte load
+template <> struct RouteVec<float> { static constexpr int N = 4; };
+template <> struct RouteVec<bf16> { static constexpr int N = 8; };
+
+__device__ __forceinline__ void route_load(const float* p, float (&v)[4]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+}
+__device__ __forceinline__ void route_load(const bf16* p, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { v[2 * i] = __bfloat162float(h2[i].x); v[2 * i + 1] = __bfloat162float(h2[i].y); }
+}
+
+template <typename T, typename W, int RB>
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const T* __restrict__ h, int ldh, const W* __restrict__ wr, int rows, int D, int E, int G, int keep,
-                 int top, float scale, int has_gate, int* __restrict__ idx, float* __restrict__ wt,
+                 int top, float scale, int has_gate, int vec_ok, int* __restrict__ idx, float* __restrict__ wt,
                  float* __restrict__ gate_out) {
   extern __shared__ float route_smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int row = blockIdx.x * (blockDim.x >> 5) + warp;
-  if (row >= rows) return;
-  float* z = route_smem + size_t(warp) * (E + 1 + G);      // scores of the experts, then the gate's logit
-  float* gb = z + E + 1;                                    // best score of each group; -1 once kept
-  const T* hr = h + size_t(row) * ldh;
-  const int outs = E + (has_gate ? 1 : 0);
-  for (int e = 0; e < outs; ++e) {
-    const W* we = wr + size_t(e) * D;
-    float acc = 0.f;
-    for (int i = lane; i < D; i += 32) acc = fmaf(ldf(hr + i), ldf(we + i), acc);
-    acc = warp_sum(acc);
-    if (lane == 0) z[e] = acc;
+  const int row0 = blockIdx.x * RB;
+  const int zstride = (E + 1 + G + 3) & ~3;                 // per row: scores, the gate's logit, the groups' best
+  float* hs = route_smem + RB * zstride;                    // RB rows of h (16-byte aligned)
+  for (int rr = 0; rr < RB; ++rr) {
+    const bool live = row0 + rr < rows;
+    const T* hr = h + size_t(live ? row0 + rr : row0) * ldh;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) hs[rr * D + i] = live ? ldf(hr + i) : 0.f;
   }
-  __syncwarp();
-  float m = -INFINITY;
-  for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
-  m = warp_max(m);
-  float sum = 0.f;
-  for (int e = lane; e < E; e += 32) sum += expf(z[e] - m);
-  sum = warp_sum(sum);
-  __syncwarp();
-  for (int e = lane; e < E; e += 32) z[e] = expf(z[e] - m) / sum;
-  if (has_gate && lane == 0) gate_out[row] = 1.f / (1.f + expf(-z[E]));
-  __syncwarp();
-  const int per = E / G;
-  const bool limited = G > 1 && keep < G;
-  if (limited) {
-    for (int g = lane; g < G; g += 32) {
-      float best = 0.f;
-      for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, z[e]);
-      gb[g] = best;
+  __syncthreads();
+  const int outs = E + (has_gate ? 1 : 0);
+  constexpr int VN = RouteVec<W>::N;
+  for (int e = warp; e < outs; e += ROUTE_WARPS) {
+    const W* we = wr + size_t(e) * D;
+    float acc[RB];
+#pragma unroll
+    for (int rr = 0; rr < RB; ++rr) acc[rr] = 0.f;
+    if (vec_ok) {
+      for (int i = lane * VN; i < D; i += 32 * VN) {
+        float v[VN];
+        route_load(we + i, v);
+#pragma unroll
+        for (int rr = 0; rr < RB; ++rr)
+#pragma unroll
+          for (int j = 0; j < VN; ++j) acc[rr] = fmaf(hs[rr * D + i + j], v[j], acc[rr]);
+      }
+    } else {
+      for (int i = lane; i < D; i += 32) {
+        const float v = ldf(we + i);
+#pragma unroll
+        for (int rr = 0; rr < RB; ++rr) acc[rr] = fmaf(hs[rr * D + i], v, acc[rr]);
+      }
     }
+#pragma unroll
+    for (int rr = 0; rr < RB; ++rr) {
+      const float a = warp_sum(acc[rr]);
+      if (lane == 0) route_smem[rr * zstride + e] = a;
+    }
+  }
+  __syncthreads();
+  for (int rr = warp; rr < RB; rr += ROUTE_WARPS) {
+    const int row = row0 + rr;
+    if (row >= rows) break;
+    float* z = route_smem + rr * zstride;
+    float* gb = z + E + 1;
+    float m = -INFINITY;
+    for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) sum += expf(z[e] - m);
+    sum = warp_sum(sum);
     __syncwarp();
-    for (int k = 0; k < keep; ++k) {
+    for (int e = lane; e < E; e += 32) z[e] = expf(z[e] - m) / sum;
+    if (has_gate && lane == 0) gate_out[row] = 1.f / (1.f + expf(-z[E]));
+    __syncwarp();
+    const int per = E / G;
+    const bool limited = G > 1 && keep < G;
+    if (limited) {
+      for (int g = lane; g < G; g += 32) {
+        float best = 0.f;
+        for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, z[e]);
+        gb[g] = best;
+      }
+      __syncwarp();
+      for (int k = 0; k < keep; ++k) {
+        float bv = -1.f;
+        int bi = 0x7fffffff;
+        for (int g = lane; g < G; g += 32)
+          if (gb[g] > bv) { bv = gb[g]; bi = g; }
+        warp_argmax(bv, bi);
+        __syncwarp();
+        if (lane == 0 && bi < G) gb[bi] = -1.f;               // kept
+        __syncwarp();
+      }
+    }
+    for (int k = 0; k < top; ++k) {
       float bv = -1.f;
       int bi = 0x7fffffff;
-      for (int g = lane; g < G; g += 32)
-        if (gb[g] > bv) { bv = gb[g]; bi = g; }
+      for (int e = lane; e < E; e += 32) {
+        const bool allowed = !limited || gb[e / per] < 0.f;
+        if (allowed && z[e] > bv) { bv = z[e]; bi = e; }
+      }
       warp_argmax(bv, bi);
       __syncwarp();
-      if (lane == 0 && bi < G) gb[bi] = -1.f;               // kept
+      if (lane == 0) {
+        const bool ok = bi < E;
+        idx[size_t(row) * top + k] = ok ? bi : 0;
+        wt[size_t(row) * top + k] = ok ? bv * scale : 0.f;
+        if (ok) z[bi] = -2.f;                                  // taken
+      }
       __syncwarp();
     }
-  }
-  for (int k = 0; k < top; ++k) {
-    float bv = -1.f;
-    int bi = 0x7fffffff;
-    for (int e = lane; e < E; e += 32) {
-      const bool allowed = !limited || gb[e / per] < 0.f;
-      if (allowed && z[e] > bv) { bv = z[e]; bi = e; }
-    }
-    warp_argmax(bv, bi);
-    __syncwarp();
-    if (lane == 0) {
-      const bool ok = bi < E;
-      idx[size_t(row) * top + k] = ok ? bi : 0;
-      wt[size_t(row) * top + k] = ok ? bv * scale : 0.f;
-      if (ok) z[bi] = -2.f;                                  // taken
-    }
-    __syncwarp();
   }
 }
 
@@ -284,16 +337,31 @@ int launch_moe_route(const void* h, int ldh, const void* wr, int w_f32, int rows
                      float scale, int has_gate, int* idx, float* wt, float* gate_out, cudaStream_t s) {
   if (rows == 0) return 0;
   if (E < 1 || G < 1 || E % G || keep < 1 || keep > G || top < 1 || top > (E / G) * keep) return KVCM_ERR_UNSUPPORTED;
-  const int warps = 4;
-  const size_t smem = size_t(warps) * (E + 1 + G) * sizeof(float);
-  if (smem > 48 * 1024) return KVCM_ERR_UNSUPPORTED;
-  const int blocks = (rows + warps - 1) / warps;
-  if (w_f32)
-    moe_route_kernel<T, float><<<blocks, warps * 32, smem, s>>>((const T*)h, ldh, (const float*)wr, rows, D, E, G, keep,
-                                                               top, scale, has_gate, idx, wt, gate_out);
-  else
-    moe_route_kernel<T, T><<<blocks, warps * 32, smem, s>>>((const T*)h, ldh, (const T*)wr, rows, D, E, G, keep, top,
-                                                           scale, has_gate, idx, wt, gate_out);
+  const size_t zstride = (size_t(E + 1 + G) + 3) & ~size_t(3);
+  int rb = rows >= 512 ? 8 : 1;                                       // many rows: read the router once for 8 of them
+  while (rb > 1 && (rb * (zstride + D)) * sizeof(float) > 160 * 1024) rb /= 2;
+  const size_t smem = rb * (zstride + D) * sizeof(float);
+  if (smem > 200 * 1024) return KVCM_ERR_UNSUPPORTED;
+  const int vec = w_f32 ? 4 : RouteVec<T>::N;
+  const int vec_ok = (D % vec) == 0 && (reinterpret_cast<uintptr_t>(wr) & 15) == 0;
+#define KVCM_ROUTE(W, RB)                                                                                             \
+  do {                                                                                                                \
+    if (smem > 48 * 1024)                                                                                             \
+      cudaFuncSetAttribute(moe_route_kernel<T, W, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+    moe_route_kernel<T, W, RB><<<(rows + RB - 1) / RB, ROUTE_WARPS * 32, smem, s>>>(                                  \
+        (const T*)h, ldh, (const W*)wr, rows, D, E, G, keep, top, scale, has_gate, vec_ok, idx, wt, gate_out);        \
+  } while (0)
+#define KVCM_ROUTE_RB(W)                                                                                              \
+  do {                                                                                                                \
+    if (rb == 8) KVCM_ROUTE(W, 8);                                                                                    \
+    else if (rb == 4) KVCM_ROUTE(W, 4);                                                                               \
+    else if (rb == 2) KVCM_ROUTE(W, 2);                                                                               \
+    else KVCM_ROUTE(W, 1);                                                                                            \
+  } while (0)
+  if (w_f32) KVCM_ROUTE_RB(float);
+  else KVCM_ROUTE_RB(T);
+#undef KVCM_ROUTE_RB
+#undef KVCM_ROUTE
   return KVCM_LAUNCH_RESULT();
 }
 
