@@ -13,8 +13,8 @@
 // Everything after the projections is float here, in both storage types.
 //
 // The columns of S are independent of each other, so the recurrence is spread over
-// (request, head, 32 columns) blocks; inside a block four lanes share a column (rows r, r+4, ...
-// each) and add their partial dot products by shuffles.  The same kernel serves portions of
+// (request, head, 32 columns) blocks; inside a block four or eight lanes share a column (rows r,
+// r + lanes, ... each) and add their partial dot products by shuffles.  The same kernel serves portions of
 // prompts and single decoded tokens: it walks the request's rows of the step in order.  The
 // recurrence is one dependent chain per column (dot product, step, update) whose length per token
 // is what bounds a long portion of ONE request; requests and heads run side by side.
@@ -81,7 +81,7 @@ delta_prepare_kernel(float* __restrict__ qkv, int channels, float* __restrict__ 
   const int row = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const float qscale = 1.f / sqrtf(float(dk));
-  for (int hh = warp; hh < 2 * qk_heads; hh += nwarps) {
+  for (int hh = blockIdx.y * nwarps + warp; hh < 2 * qk_heads; hh += gridDim.y * nwarps) {
     float* p = qkv + size_t(row) * channels + size_t(hh) * dk;
     float ss = 0.f;
     for (int i = lane; i < dk; i += 32) ss += p[i] * p[i];
@@ -90,7 +90,7 @@ delta_prepare_kernel(float* __restrict__ qkv, int channels, float* __restrict__ 
     if (hh < qk_heads) inv *= qscale;
     for (int i = lane; i < dk; i += 32) p[i] *= inv;
   }
-  for (int h = threadIdx.x; h < heads; h += blockDim.x) {
+  for (int h = blockIdx.y * blockDim.x + threadIdx.x; h < heads; h += gridDim.y * blockDim.x) {
     float* r = ba + size_t(row) * 2 * heads;
     const float b = r[h];
     const float a = r[heads + h] + dt_bias[h];
@@ -102,7 +102,6 @@ delta_prepare_kernel(float* __restrict__ qkv, int channels, float* __restrict__ 
 
 // ------------------------------------------------------------------------------ the recurrence
 constexpr int DR_COLS = 32;      // columns of S per block
-constexpr int DR_LANES = 4;      // lanes that share a column
 
 // 4 bytes from global to shared memory without passing through registers; `ok` false writes zero.
 __device__ __forceinline__ void dr_copy4(float* dst, const float* src, bool ok) {
@@ -111,17 +110,20 @@ __device__ __forceinline__ void dr_copy4(float* dst, const float* src, bool ok) 
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(d), "l"(src), "r"(bytes) : "memory");
 }
 
-// NI: rows of S per thread (dk <= 4 * NI).  TT tokens are staged in shared memory at a time, in two
-// buffers: while one tile of tokens is worked through, the next is on its way (cp.async).
-template <int NI, int TT>
+// DR_LANES lanes share a column; NI: rows of S per thread (dk <= DR_LANES * NI).  TT tokens are staged
+// in shared memory at a time, in two buffers: while one tile of tokens is worked through, the next is
+// on its way (cp.async).  Eight lanes a column for the longer keys: shorter chains of dependent FMAs
+// per token and twice the warps to hide them behind.
+template <int DR_LANES, int NI, int TT>
 __global__ void __launch_bounds__(DR_COLS * DR_LANES)
 delta_scan_kernel(const float* __restrict__ qkv, int channels, const float* __restrict__ bg,
                   float* __restrict__ state, long long state_stride, const int* __restrict__ seq_q_start,
                   const int* __restrict__ seq_q_len, const int* __restrict__ seq_state_slot,
                   float* __restrict__ out, int heads, int qk_heads, int dk, int dv) {
   constexpr int DKP = DR_LANES * NI;
-  constexpr int NIP = NI + 4;      // a lane's NI values lie together (element i = r + 4 m at [i % 4][i / 4]); the pad
-                                   // puts the four lanes' 16-byte loads on different banks
+  constexpr int NIP = NI + 4;      // a lane's NI values lie together (element i = r + LANES m at [i % LANES][i / LANES]);
+                                   // the pad puts the lanes' 16-byte loads on different banks
+  constexpr int CPW = 32 / DR_LANES;                      // columns per warp
   __shared__ __align__(16) float qs[2][TT][DR_LANES][NIP];
   __shared__ __align__(16) float ks[2][TT][DR_LANES][NIP];
   __shared__ float vs[2][TT][DR_COLS];
@@ -132,9 +134,9 @@ delta_scan_kernel(const float* __restrict__ qkv, int channels, const float* __re
   const int q0 = seq_q_start[s], n = seq_q_len[s];
   const int qk_head = head / (heads / qk_heads);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int col_local = warp * 8 + (lane & 7);
+  const int col_local = warp * CPW + (lane % CPW);
   const int col = blockIdx.x * DR_COLS + col_local;
-  const int r = lane >> 3;
+  const int r = lane / CPW;
   const bool col_ok = col < dv;
   float* S = state + slot * state_stride + (size_t(head) * dk) * dv + col;
   float acc[NI];
@@ -195,8 +197,8 @@ delta_scan_kernel(const float* __restrict__ qkv, int channels, const float* __re
 #pragma unroll
       for (int m = 0; m < NI; ++m) p4[m & 3] = fmaf(acc[m], kt[m], p4[m & 3]);
       float p = (p4[0] + p4[1]) + (p4[2] + p4[3]);
-      p += __shfl_xor_sync(0xffffffffu, p, 8);
-      p += __shfl_xor_sync(0xffffffffu, p, 16);
+#pragma unroll
+      for (int w = CPW; w < 32; w <<= 1) p += __shfl_xor_sync(0xffffffffu, p, w);
       const float u = beta * (vs[buf][t][col_local] - g * p);
       float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -205,8 +207,8 @@ delta_scan_kernel(const float* __restrict__ qkv, int channels, const float* __re
         o4[m & 3] = fmaf(acc[m], qt[m], o4[m & 3]);
       }
       float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
-      o += __shfl_xor_sync(0xffffffffu, o, 8);
-      o += __shfl_xor_sync(0xffffffffu, o, 16);
+#pragma unroll
+      for (int w = CPW; w < 32; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
       if (r == 0 && col_ok) out[size_t(q0 + t0 + t) * heads * dv + size_t(head) * dv + col] = o;
     }
   }
@@ -225,7 +227,7 @@ gated_rms_kernel(const float* __restrict__ o, const T* __restrict__ gate, int ld
                  T* __restrict__ out, int heads, int dv, float eps) {
   const int row = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  for (int h = warp; h < heads; h += nwarps) {
+  for (int h = blockIdx.y * nwarps + warp; h < heads; h += gridDim.y * nwarps) {
     const float* p = o + size_t(row) * heads * dv + size_t(h) * dv;
     float ss = 0.f;
     for (int j = lane; j < dv; j += 32) ss += p[j] * p[j];
@@ -276,30 +278,32 @@ KVCM_API int kvcm_delta_conv_bf16(const void* proj, int ldp, const float* conv_w
 KVCM_API int kvcm_delta_prepare(float* qkv, int channels, float* ba, const float* a_log, const float* dt_bias,
                                 int rows, int heads, int qk_heads, int dk, void* stream) {
   if (rows == 0) return 0;
-  delta_prepare_kernel<<<rows, 128, 0, (cudaStream_t)stream>>>(qkv, channels, ba, a_log, dt_bias, heads, qk_heads, dk);
+  // a warp per query/key head: few rows (decode) get a block for every four heads
+  const int by = rows < 256 ? (2 * qk_heads + 3) / 4 : 1;
+  delta_prepare_kernel<<<dim3(rows, by), 128, 0, (cudaStream_t)stream>>>(qkv, channels, ba, a_log, dt_bias, heads, qk_heads, dk);
   return KVCM_LAUNCH_RESULT();
 }
 
 // Largest key size the recurrence kernel holds in registers.
-KVCM_API int kvcm_delta_scan_max_dk() { return DR_LANES * 64; }
+KVCM_API int kvcm_delta_scan_max_dk() { return 256; }
 
 KVCM_API int kvcm_delta_scan(const float* qkv, int channels, const float* bg, float* state, long long state_stride,
                              const int* seq_q_start, const int* seq_q_len, const int* seq_state_slot, float* out,
                              int seqs, int heads, int qk_heads, int dk, int dv, void* stream) {
   if (seqs == 0) return 0;
-  if (dk < 1 || dk > DR_LANES * 64 || qk_heads < 1 || heads % qk_heads) return KVCM_ERR_UNSUPPORTED;
-  const dim3 grid((dv + DR_COLS - 1) / DR_COLS, heads, seqs), block(DR_COLS * DR_LANES);
+  if (dk < 1 || dk > 256 || qk_heads < 1 || heads % qk_heads) return KVCM_ERR_UNSUPPORTED;
+  const dim3 grid((dv + DR_COLS - 1) / DR_COLS, heads, seqs);
   cudaStream_t s = (cudaStream_t)stream;
-#define KVCM_SCAN(NI, TT)                                                                                          \
-  delta_scan_kernel<NI, TT><<<grid, block, 0, s>>>(qkv, channels, bg, state, state_stride, seq_q_start, seq_q_len, \
-                                                   seq_state_slot, out, heads, qk_heads, dk, dv)
-  const int need = (dk + DR_LANES - 1) / DR_LANES;
-  if (need <= 2) KVCM_SCAN(2, 16);
-  else if (need <= 4) KVCM_SCAN(4, 16);
-  else if (need <= 8) KVCM_SCAN(8, 16);
-  else if (need <= 16) KVCM_SCAN(16, 16);
-  else if (need <= 32) KVCM_SCAN(32, 16);
-  else KVCM_SCAN(64, 8);
+#define KVCM_SCAN(LANES, NI, TT)                                                                                   \
+  delta_scan_kernel<LANES, NI, TT><<<grid, DR_COLS * LANES, 0, s>>>(qkv, channels, bg, state, state_stride,        \
+                                                                   seq_q_start, seq_q_len, seq_state_slot, out,    \
+                                                                   heads, qk_heads, dk, dv)
+  if (dk <= 8) KVCM_SCAN(4, 2, 16);
+  else if (dk <= 16) KVCM_SCAN(4, 4, 16);
+  else if (dk <= 32) KVCM_SCAN(4, 8, 16);
+  else if (dk <= 64) KVCM_SCAN(8, 8, 16);
+  else if (dk <= 128) KVCM_SCAN(8, 16, 16);
+  else KVCM_SCAN(8, 32, 8);
 #undef KVCM_SCAN
   return KVCM_LAUNCH_RESULT();
 }
@@ -307,12 +311,14 @@ KVCM_API int kvcm_delta_scan(const float* qkv, int channels, const float* bg, fl
 KVCM_API int kvcm_gated_rms_f32(const float* o, const void* gate, int ldg, const float* w, void* out, int rows,
                                 int heads, int dv, float eps, void* stream) {
   if (rows == 0) return 0;
-  gated_rms_kernel<float><<<rows, 128, 0, (cudaStream_t)stream>>>(o, (const float*)gate, ldg, w, (float*)out, heads, dv, eps);
+  gated_rms_kernel<float><<<dim3(rows, rows < 256 ? (heads + 3) / 4 : 1), 128, 0, (cudaStream_t)stream>>>(
+      o, (const float*)gate, ldg, w, (float*)out, heads, dv, eps);
   return KVCM_LAUNCH_RESULT();
 }
 KVCM_API int kvcm_gated_rms_bf16(const float* o, const void* gate, int ldg, const float* w, void* out, int rows,
                                  int heads, int dv, float eps, void* stream) {
   if (rows == 0) return 0;
-  gated_rms_kernel<bf16><<<rows, 128, 0, (cudaStream_t)stream>>>(o, (const bf16*)gate, ldg, w, (bf16*)out, heads, dv, eps);
+  gated_rms_kernel<bf16><<<dim3(rows, rows < 256 ? (heads + 3) / 4 : 1), 128, 0, (cudaStream_t)stream>>>(
+      o, (const bf16*)gate, ldg, w, (bf16*)out, heads, dv, eps);
   return KVCM_LAUNCH_RESULT();
 }

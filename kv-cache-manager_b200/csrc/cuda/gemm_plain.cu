@@ -64,6 +64,42 @@ gemm_plain_kernel(const TIn* __restrict__ X, const TIn* __restrict__ W, TOut* __
   }
 }
 
+// A batch of products of a handful of rows (decode): one warp per output column n of one product,
+// the lanes stride over k with float FMAs in a fixed order, at most 16 rows at a time.  The rows of
+// X (for this product) are staged in shared memory as floats.
+constexpr int kFewRows = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+gemm_few_rows_kernel(const T* __restrict__ X, const T* __restrict__ W, T* __restrict__ Y, int M, int N, int K,
+                     int ldx, int ldw, int ldy, long long bx, long long bw, long long by) {
+  extern __shared__ float xrows[];                 // [M][K]
+  X += blockIdx.z * bx;
+  W += blockIdx.z * bw;
+  Y += blockIdx.z * by;
+  for (int i = threadIdx.x; i < M * K; i += blockDim.x) xrows[i] = ldf(X + size_t(i / K) * ldx + i % K);
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (n >= N) return;
+  float acc[kFewRows];
+#pragma unroll
+  for (int m = 0; m < kFewRows; ++m) acc[m] = 0.f;
+  const T* wn = W + size_t(n) * ldw;
+  for (int k = lane; k < K; k += 32) {
+    const float w = ldf(wn + k);
+#pragma unroll
+    for (int m = 0; m < kFewRows; ++m)
+      if (m < M) acc[m] = fmaf(xrows[m * K + k], w, acc[m]);
+  }
+#pragma unroll
+  for (int m = 0; m < kFewRows; ++m) {
+    if (m >= M) break;
+    const float a = warp_sum(acc[m]);
+    if (lane == 0) stf(Y + size_t(m) * ldy + n, a);
+  }
+}
+
 template <typename TIn, typename TOut>
 int launch_gemm_plain(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw,
                       int ldy, cudaStream_t s, int batch = 1, long long bx = 0, long long bw = 0, long long by = 0) {
@@ -94,11 +130,27 @@ KVCM_API int kvcm_gemm_plain_bf16_f32out(const void* X, const void* W, void* Y, 
 
 // A batch of such products in one launch (one per head, say): product z reads X + z*bx and
 // W + z*bw and writes Y + z*by (element counts); rows ldx / ldw / ldy apart as above.
+template <typename T>
+int launch_gemm_few_rows(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy, int batch,
+                         long long bx, long long bw, long long by, cudaStream_t s) {
+  const size_t smem = size_t(M) * K * sizeof(float);
+  gemm_few_rows_kernel<T><<<dim3((N + 7) / 8, 1, batch), 256, smem, s>>>((const T*)X, (const T*)W, (T*)Y, M, N, K, ldx, ldw,
+                                                                        ldy, bx, bw, by);
+  return KVCM_LAUNCH_RESULT();
+}
+static bool few_rows(int M, int N, int K, int batch) {
+  return M >= 1 && M <= kFewRows && size_t(M) * K * sizeof(float) <= 48 * 1024 && batch >= 1 && batch <= 65535 && N >= 1;
+}
+
 KVCM_API int kvcm_gemm_plain_batched_f32(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw,
                                          int ldy, int batch, long long bx, long long bw, long long by, void* stream) {
+  if (few_rows(M, N, K, batch))
+    return launch_gemm_few_rows<float>(X, W, Y, M, N, K, ldx, ldw, ldy, batch, bx, bw, by, (cudaStream_t)stream);
   return launch_gemm_plain<float, float>(X, W, Y, M, N, K, ldx, ldw, ldy, (cudaStream_t)stream, batch, bx, bw, by);
 }
 KVCM_API int kvcm_gemm_plain_batched_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw,
                                           int ldy, int batch, long long bx, long long bw, long long by, void* stream) {
+  if (few_rows(M, N, K, batch))
+    return launch_gemm_few_rows<bf16>(X, W, Y, M, N, K, ldx, ldw, ldy, batch, bx, bw, by, (cudaStream_t)stream);
   return launch_gemm_plain<bf16, bf16>(X, W, Y, M, N, K, ldx, ldw, ldy, (cudaStream_t)stream, batch, bx, bw, by);
 }

@@ -42,6 +42,7 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 // RB rows), then warp w does the softmax and the choice of rows w, w + 8, ...  RB = 1 for steps of
 // few rows (more blocks), up to 8 for many (the router matrix is read once per block).
 constexpr int ROUTE_WARPS = 8;
+constexpr int ROUTE_EG = 4;      // experts a warp works on at a time
 
 template <typename W> struct RouteVec;                     // elements of a 16-byte load
 template <> struct RouteVec<float> { static constexpr int N = 4; };
@@ -76,32 +77,53 @@ moe_route_kernel(const T* __restrict__ h, int ldh, const W* __restrict__ wr, int
   __syncthreads();
   const int outs = E + (has_gate ? 1 : 0);
   constexpr int VN = RouteVec<W>::N;
-  for (int e = warp; e < outs; e += ROUTE_WARPS) {
-    const W* we = wr + size_t(e) * D;
-    float acc[RB];
+  // A warp takes ROUTE_EG neighbouring experts at a time: a piece of the rows of h is read from shared
+  // memory once for all of them, and their pieces of the router's rows are requested together.
+  for (int e0 = warp * ROUTE_EG; e0 < outs; e0 += ROUTE_WARPS * ROUTE_EG) {
+    float acc[ROUTE_EG][RB];
 #pragma unroll
-    for (int rr = 0; rr < RB; ++rr) acc[rr] = 0.f;
+    for (int k = 0; k < ROUTE_EG; ++k)
+#pragma unroll
+      for (int rr = 0; rr < RB; ++rr) acc[k][rr] = 0.f;
     if (vec_ok) {
+#pragma unroll 2
       for (int i = lane * VN; i < D; i += 32 * VN) {
-        float v[VN];
-        route_load(we + i, v);
+        float v[ROUTE_EG][VN];
 #pragma unroll
-        for (int rr = 0; rr < RB; ++rr)
+        for (int k = 0; k < ROUTE_EG; ++k)
+          route_load(wr + size_t(min(e0 + k, outs - 1)) * D + i, v[k]);
 #pragma unroll
-          for (int j = 0; j < VN; ++j) acc[rr] = fmaf(hs[rr * D + i + j], v[j], acc[rr]);
+        for (int rr = 0; rr < RB; ++rr) {
+          float hv[VN];
+#pragma unroll
+          for (int j = 0; j < VN; j += 4) {
+            const float4 a = *reinterpret_cast<const float4*>(hs + rr * D + i + j);
+            hv[j] = a.x; hv[j + 1] = a.y; hv[j + 2] = a.z; hv[j + 3] = a.w;
+          }
+#pragma unroll
+          for (int k = 0; k < ROUTE_EG; ++k)
+#pragma unroll
+            for (int j = 0; j < VN; ++j) acc[k][rr] = fmaf(hv[j], v[k][j], acc[k][rr]);
+        }
       }
     } else {
       for (int i = lane; i < D; i += 32) {
-        const float v = ldf(we + i);
+        float v[ROUTE_EG];
 #pragma unroll
-        for (int rr = 0; rr < RB; ++rr) acc[rr] = fmaf(hs[rr * D + i], v, acc[rr]);
+        for (int k = 0; k < ROUTE_EG; ++k) v[k] = ldf(wr + size_t(min(e0 + k, outs - 1)) * D + i);
+#pragma unroll
+        for (int rr = 0; rr < RB; ++rr)
+#pragma unroll
+          for (int k = 0; k < ROUTE_EG; ++k) acc[k][rr] = fmaf(hs[rr * D + i], v[k], acc[k][rr]);
       }
     }
 #pragma unroll
-    for (int rr = 0; rr < RB; ++rr) {
-      const float a = warp_sum(acc[rr]);
-      if (lane == 0) route_smem[rr * zstride + e] = a;
-    }
+    for (int k = 0; k < ROUTE_EG; ++k)
+#pragma unroll
+      for (int rr = 0; rr < RB; ++rr) {
+        const float a = warp_sum(acc[k][rr]);
+        if (lane == 0 && e0 + k < outs) route_smem[rr * zstride + e0 + k] = a;
+      }
   }
   __syncthreads();
   for (int rr = warp; rr < RB; rr += ROUTE_WARPS) {
@@ -322,12 +344,24 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place_of, const float* __restrict__ wt, int top,
                    const float* __restrict__ shared_y, const float* __restrict__ gate, float* __restrict__ out, int D) {
+  constexpr int KMAX = 8;                                  // choices whose places and weights are kept in registers
   const int row = blockIdx.x;
+  int place[KMAX];
+  float w[KMAX];
+#pragma unroll
+  for (int k = 0; k < KMAX; ++k) {
+    place[k] = k < top ? place_of[size_t(row) * top + k] : 0;
+    w[k] = k < top ? wt[size_t(row) * top + k] : 0.f;
+  }
+  const float gt = shared_y ? (gate ? gate[row] : 1.f) : 0.f;
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
     float acc = 0.f;
-    for (int k = 0; k < top; ++k)
+#pragma unroll
+    for (int k = 0; k < KMAX; ++k)
+      if (k < top) acc = fmaf(w[k], y[size_t(place[k]) * D + i], acc);
+    for (int k = KMAX; k < top; ++k)
       acc = fmaf(wt[size_t(row) * top + k], y[size_t(place_of[size_t(row) * top + k]) * D + i], acc);
-    if (shared_y) acc += (gate ? gate[row] : 1.f) * shared_y[size_t(row) * D + i];
+    if (shared_y) acc += gt * shared_y[size_t(row) * D + i];
     out[size_t(row) * D + i] = acc;
   }
 }
