@@ -101,7 +101,6 @@ delta_prepare_kernel(float* __restrict__ qkv, int channels, float* __restrict__ 
 }
 
 // ------------------------------------------------------------------------------ the recurrence
-constexpr int DR_COLS = 32;      // columns of S per block
 
 // 4 bytes from global to shared memory without passing through registers; `ok` false writes zero.
 __device__ __forceinline__ void dr_copy4(float* dst, const float* src, bool ok) {
@@ -114,7 +113,8 @@ __device__ __forceinline__ void dr_copy4(float* dst, const float* src, bool ok) 
 // in shared memory at a time, in two buffers: while one tile of tokens is worked through, the next is
 // on its way (cp.async).  Eight lanes a column for the longer keys: shorter chains of dependent FMAs
 // per token and twice the warps to hide them behind.
-template <int DR_LANES, int NI, int TT>
+// DR_COLS columns of S per block: 32, or fewer where that many blocks would leave SMs idle.
+template <int DR_COLS, int DR_LANES, int NI, int TT>
 __global__ void __launch_bounds__(DR_COLS * DR_LANES)
 delta_scan_kernel(const float* __restrict__ qkv, int channels, const float* __restrict__ bg,
                   float* __restrict__ state, long long state_stride, const int* __restrict__ seq_q_start,
@@ -292,12 +292,25 @@ KVCM_API int kvcm_delta_scan(const float* qkv, int channels, const float* bg, fl
                              int seqs, int heads, int qk_heads, int dk, int dv, void* stream) {
   if (seqs == 0) return 0;
   if (dk < 1 || dk > 256 || qk_heads < 1 || heads % qk_heads) return KVCM_ERR_UNSUPPORTED;
-  const dim3 grid((dv + DR_COLS - 1) / DR_COLS, heads, seqs);
   cudaStream_t s = (cudaStream_t)stream;
-#define KVCM_SCAN(LANES, NI, TT)                                                                                   \
-  delta_scan_kernel<LANES, NI, TT><<<grid, DR_COLS * LANES, 0, s>>>(qkv, channels, bg, state, state_stride,        \
-                                                                   seq_q_start, seq_q_len, seq_state_slot, out,    \
-                                                                   heads, qk_heads, dk, dv)
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  // 32 columns a block; 16 or 8 when that leaves SMs without a block (one request's long portion)
+  const long long per32 = (long long)seqs * heads * ((dv + 31) / 32);
+  const int cols = per32 >= sms ? 32 : (2 * per32 >= sms ? 16 : 8);
+#define KVCM_SCAN_C(COLS, LANES, NI, TT)                                                                            \
+  delta_scan_kernel<COLS, LANES, NI, TT><<<dim3((dv + COLS - 1) / COLS, heads, seqs), COLS * LANES, 0, s>>>(         \
+      qkv, channels, bg, state, state_stride, seq_q_start, seq_q_len, seq_state_slot, out, heads, qk_heads, dk, dv)
+#define KVCM_SCAN(LANES, NI, TT)                                                                                    \
+  do {                                                                                                              \
+    if (cols == 32) KVCM_SCAN_C(32, LANES, NI, TT);                                                                 \
+    else if (cols == 16) KVCM_SCAN_C(16, LANES, NI, TT);                                                            \
+    else KVCM_SCAN_C(8, LANES, NI, TT);                                                                             \
+  } while (0)
   if (dk <= 8) KVCM_SCAN(4, 2, 16);
   else if (dk <= 16) KVCM_SCAN(4, 4, 16);
   else if (dk <= 32) KVCM_SCAN(4, 8, 16);
@@ -305,6 +318,7 @@ KVCM_API int kvcm_delta_scan(const float* qkv, int channels, const float* bg, fl
   else if (dk <= 128) KVCM_SCAN(8, 16, 16);
   else KVCM_SCAN(8, 32, 8);
 #undef KVCM_SCAN
+#undef KVCM_SCAN_C
   return KVCM_LAUNCH_RESULT();
 }
 

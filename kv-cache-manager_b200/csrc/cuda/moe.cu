@@ -344,24 +344,12 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place_of, const float* __restrict__ wt, int top,
                    const float* __restrict__ shared_y, const float* __restrict__ gate, float* __restrict__ out, int D) {
-  constexpr int KMAX = 8;                                  // choices whose places and weights are kept in registers
   const int row = blockIdx.x;
-  int place[KMAX];
-  float w[KMAX];
-#pragma unroll
-  for (int k = 0; k < KMAX; ++k) {
-    place[k] = k < top ? place_of[size_t(row) * top + k] : 0;
-    w[k] = k < top ? wt[size_t(row) * top + k] : 0.f;
-  }
-  const float gt = shared_y ? (gate ? gate[row] : 1.f) : 0.f;
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
     float acc = 0.f;
-#pragma unroll
-    for (int k = 0; k < KMAX; ++k)
-      if (k < top) acc = fmaf(w[k], y[size_t(place[k]) * D + i], acc);
-    for (int k = KMAX; k < top; ++k)
+    for (int k = 0; k < top; ++k)
       acc = fmaf(wt[size_t(row) * top + k], y[size_t(place_of[size_t(row) * top + k]) * D + i], acc);
-    if (shared_y) acc += gt * shared_y[size_t(row) * D + i];
+    if (shared_y) acc += (gate ? gate[row] : 1.f) * shared_y[size_t(row) * D + i];
     out[size_t(row) * D + i] = acc;
   }
 }
