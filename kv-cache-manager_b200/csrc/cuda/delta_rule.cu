@@ -278,8 +278,7 @@ KVCM_API int kvcm_delta_conv_bf16(const void* proj, int ldp, const float* conv_w
 KVCM_API int kvcm_delta_prepare(float* qkv, int channels, float* ba, const float* a_log, const float* dt_bias,
                                 int rows, int heads, int qk_heads, int dk, void* stream) {
   if (rows == 0) return 0;
-  // a warp per query/key head: few rows (decode) get a block for every four heads
-  const int by = rows < 256 ? (2 * qk_heads + 3) / 4 : 1;
+  const int by = (2 * qk_heads + 3) / 4;                       // a warp per query/key head, four to a block
   delta_prepare_kernel<<<dim3(rows, by), 128, 0, (cudaStream_t)stream>>>(qkv, channels, ba, a_log, dt_bias, heads, qk_heads, dk);
   return KVCM_LAUNCH_RESULT();
 }
@@ -287,9 +286,12 @@ KVCM_API int kvcm_delta_prepare(float* qkv, int channels, float* ba, const float
 // Largest key size the recurrence kernel holds in registers.
 KVCM_API int kvcm_delta_scan_max_dk() { return 256; }
 
+// `rows`: rows of the step.  When every request brings one row (rows == seqs) the kernel is bound by
+// reading and writing the state: four lanes a column then, so that a warp's access covers whole
+// 32-byte sectors of a row of S.
 KVCM_API int kvcm_delta_scan(const float* qkv, int channels, const float* bg, float* state, long long state_stride,
                              const int* seq_q_start, const int* seq_q_len, const int* seq_state_slot, float* out,
-                             int seqs, int heads, int qk_heads, int dk, int dv, void* stream) {
+                             int rows, int seqs, int heads, int qk_heads, int dk, int dv, void* stream) {
   if (seqs == 0) return 0;
   if (dk < 1 || dk > 256 || qk_heads < 1 || heads % qk_heads) return KVCM_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
@@ -311,11 +313,12 @@ KVCM_API int kvcm_delta_scan(const float* qkv, int channels, const float* bg, fl
     else if (cols == 16) KVCM_SCAN_C(16, LANES, NI, TT);                                                            \
     else KVCM_SCAN_C(8, LANES, NI, TT);                                                                             \
   } while (0)
+  const bool single_rows = rows == seqs;
   if (dk <= 8) KVCM_SCAN(4, 2, 16);
   else if (dk <= 16) KVCM_SCAN(4, 4, 16);
   else if (dk <= 32) KVCM_SCAN(4, 8, 16);
-  else if (dk <= 64) KVCM_SCAN(8, 8, 16);
-  else if (dk <= 128) KVCM_SCAN(8, 16, 16);
+  else if (dk <= 64) { if (single_rows) KVCM_SCAN(4, 16, 16); else KVCM_SCAN(8, 8, 16); }
+  else if (dk <= 128) { if (single_rows) KVCM_SCAN(4, 32, 16); else KVCM_SCAN(8, 16, 16); }
   else KVCM_SCAN(8, 32, 8);
 #undef KVCM_SCAN
 #undef KVCM_SCAN_C
@@ -325,14 +328,14 @@ KVCM_API int kvcm_delta_scan(const float* qkv, int channels, const float* bg, fl
 KVCM_API int kvcm_gated_rms_f32(const float* o, const void* gate, int ldg, const float* w, void* out, int rows,
                                 int heads, int dv, float eps, void* stream) {
   if (rows == 0) return 0;
-  gated_rms_kernel<float><<<dim3(rows, rows < 256 ? (heads + 3) / 4 : 1), 128, 0, (cudaStream_t)stream>>>(
+  gated_rms_kernel<float><<<dim3(rows, (heads + 3) / 4), 128, 0, (cudaStream_t)stream>>>(
       o, (const float*)gate, ldg, w, (float*)out, heads, dv, eps);
   return KVCM_LAUNCH_RESULT();
 }
 KVCM_API int kvcm_gated_rms_bf16(const float* o, const void* gate, int ldg, const float* w, void* out, int rows,
                                  int heads, int dv, float eps, void* stream) {
   if (rows == 0) return 0;
-  gated_rms_kernel<bf16><<<dim3(rows, rows < 256 ? (heads + 3) / 4 : 1), 128, 0, (cudaStream_t)stream>>>(
+  gated_rms_kernel<bf16><<<dim3(rows, (heads + 3) / 4), 128, 0, (cudaStream_t)stream>>>(
       o, (const bf16*)gate, ldg, w, (bf16*)out, heads, dv, eps);
   return KVCM_LAUNCH_RESULT();
 }

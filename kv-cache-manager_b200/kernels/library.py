@@ -975,7 +975,7 @@ def delta_scan(qkv: torch.Tensor, bg: torch.Tensor, state: torch.Tensor, ctx, ou
     _need(qkv.shape[1] == 2 * qk_heads * dk + heads * dv and out.shape == (qkv.shape[0], heads * dv)
           and state.shape[1] >= heads * dk * dv, "delta_scan: shapes")
     _check(_lib().kvcm_delta_scan(_p(qkv), qkv.shape[1], _p(bg), _p(state), _ll(state.stride(0)), _p(ctx.seq_q_start),
-                                  _p(ctx.seq_q_len), _p(ctx.seq_state_slot), _p(out), ctx.seqs, heads, qk_heads, dk, dv,
+                                  _p(ctx.seq_q_len), _p(ctx.seq_state_slot), _p(out), qkv.shape[0], ctx.seqs, heads, qk_heads, dk, dv,
                                   _stream()), "delta_scan", f"(dk={dk}, dv={dv})")
 
 
