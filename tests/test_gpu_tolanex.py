@@ -242,6 +242,32 @@ def test_pair_table_and_positions_of_the_embedding():
     assert P.bigram_rows([49999, 3], buckets, mp, mc) == rows[:2]
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("layer", [
+    {"type": "delta", "mixer": {"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 48, "conv": 4}, "mlp": None},
+    {"type": "delta", "mixer": {"heads": 2, "kv_heads": 2, "dim": 128, "vdim": 128, "conv": 2}, "mlp": None},
+    {"type": "delta", "mixer": {"heads": 2, "kv_heads": 1, "dim": 200, "vdim": 36, "conv": 3}, "mlp": None},
+    {"type": "latent_attention", "mixer": {"heads": 4, "dim": 32, "vdim": 24, "kv_rank": 64, "scale": 0.2}, "mlp": None},
+    {"type": "latent_attention", "mixer": {"heads": 6, "dim": 64, "vdim": 64, "kv_rank": 128, "scale": 0.125}, "mlp": None},
+    {"type": "latent_attention", "mixer": {"heads": 3, "dim": 16, "vdim": 16, "kv_rank": 256, "scale": 0.25}, "mlp": None},
+], ids=["delta-64", "delta-128", "delta-200", "latent-64", "latent-128", "latent-256"])
+def test_mixers_at_the_sizes_of_the_fast_kernels(tmp_path, layer, dtype):
+    """Key sizes that take the other forms of the recurrence kernel (8 lanes a column; more rows of
+    S per thread) and ranks that take the tensor-core attention kernels with all heads on one shared
+    head (tcgen05 for 64 and 128, mma.sync for 256): 300 tokens whole, then a prompt with 40 single
+    tokens behind it."""
+    folder = one_layer_model(tmp_path, layer, dtype, width=96, max_positions=320,
+                             embedding={"bigram": {"buckets": 11, "mul_prev": 3, "mul_cur": 5}})
+    toks = helpers.random_tokens(300, 120, 17)
+    ref = TM.plain_logits(folder, toks)
+    r = helpers.Replayer(folder, dtype, 640, 16)
+    whole = r.step([dict(id="a", tokens=toks, want=list(range(300)))], end=["a"])
+    close(whole, ref, dtype, "whole")
+    outs = [r.step([dict(id="b", tokens=toks[:260], want=list(range(260)))])]
+    outs += [r.step([dict(id="b", tokens=[t], want=[0])]) for t in toks[260:]]
+    close(torch.cat(outs), ref, dtype, "prompt, then single tokens")
+
+
 # ------------------------------------------------------------------ keys far away, at page borders
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
