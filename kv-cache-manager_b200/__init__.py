@@ -1,5 +1,5 @@
-"""kvcm: a small, whole, single-GPU inference engine for the Llama dense decoder on B200
-(sm_100a), with the capabilities of the kvpage reference: typed config and registry, weights
+"""kvcm: a small, whole, single-GPU inference engine for the Llama dense decoder and for Tolanex
+(gated delta rule, attention over a cached latent, routed experts) on B200 (sm_100a), with the capabilities of the kvpage reference: typed config and registry, weights
 from safetensors, layers put together from parts, a paged cache manager, one step function for
 mixed batches, a continuous-batching scheduler with chunked prefill, sampling, hand-written CUDA
 kernels, a true float32 path and trace replay.

@@ -20,8 +20,31 @@ def engine_config_from_args(a):
                         sampling_seed=a.i64("sampling-seed", 0), cuda_graphs=not a.flag("no-graphs"))
 
 
+def _tolanex_mini():
+    """A small Tolanex: delta, latent attention, a latent layer reading the one before, delta; experts on
+    three of the four layers."""
+    def mlp(shared):
+        m = {"kind": "moe", "expert": {"ff": 128},
+             "router": {"experts": 16, "top": 2, "scale": 1.5, "groups": {"count": 4, "keep": 2}}}
+        if shared:
+            m["shared"] = {"ff": shared}
+        return m
+    return {"architecture": "Tolanex", "vocab": 1000, "width": 384, "max_positions": 1024, "norm": {"eps": 1e-5},
+            "residual_mult": 0.6, "embedding": {"bigram": {"buckets": 1021, "mul_prev": 31, "mul_cur": 7}},
+            "layers": [
+                {"type": "delta", "mixer": {"heads": 6, "kv_heads": 3, "dim": 64, "vdim": 64, "conv": 4}, "mlp": mlp(256)},
+                {"type": "latent_attention", "mixer": {"heads": 6, "dim": 32, "vdim": 64, "kv_rank": 64, "scale": 0.18},
+                 "mlp": mlp(0)},
+                {"type": "latent_attention", "mixer": {"heads": 4, "dim": 32, "vdim": 32, "kv_rank": 64, "scale": 0.18,
+                                                        "kv_from": 1}, "mlp": None},
+                {"type": "delta", "mixer": {"heads": 4, "kv_heads": 4, "dim": 32, "vdim": 96, "conv": 2}, "mlp": mlp(128)},
+            ]}
+
+
 PRESETS = {
-    # name: (config.json keys of a Llama dense decoder, seed, norm jitter)
+    # name: (config.json keys, seed, norm jitter); keys with "architecture" go through the registry,
+    # the others are those of a Llama dense decoder
+    "tolanex-mini": (_tolanex_mini(), 4, 0.1),
     "tiny-a": (dict(vocab_size=256, hidden_size=64, intermediate_size=172, num_hidden_layers=2,
                     num_attention_heads=4, num_key_value_heads=2, head_dim=16, max_position_embeddings=128,
                     rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False), 0, 0.0),
@@ -64,7 +87,11 @@ def load_model_from_args(a, dtype: str, device: str = "cuda:0", stored_as: str =
     if preset not in PRESETS:
         raise SystemExit(f"unknown preset '{preset}'; known: {', '.join(PRESETS)}")
     keys, seed, jitter = PRESETS[preset]
-    cfg = LlamaConfig(architecture="LlamaForCausalLM", **keys)
+    if "architecture" in keys:
+        from ..config import config_from_dict
+        cfg = config_from_dict(keys)
+    else:
+        cfg = LlamaConfig(architecture="LlamaForCausalLM", **keys)
     seed = a.i64("random-seed", seed)
     tensors = dict(random_tensors(cfg, seed, torch_dtype(stored_as or dtype), device=device, norm_jitter=jitter))
     if stored_as and stored_as != dtype:

@@ -382,6 +382,8 @@ PYBIND11_MODULE(kvcm_core, m) {
       .def("counters", &Scheduler::counters)
       .def("reset_counters", &Scheduler::reset_counters)
       .def("slots_taken", [](const Scheduler& s) { return s.slots().num_taken(); })
+      .def("borrow_slot", &Scheduler::borrow_slot)
+      .def("return_slot", &Scheduler::return_slot)
       .def("kv_stats", [](Scheduler& s) { return s.kv().stats(s.live()); });
 
   // ---- the request loop in C++ (native_engine.h)

@@ -66,6 +66,9 @@ class Scheduler {
   void reset_counters() { ctr_ = {}; }
   KVManager& kv() { return kv_; }
   const StateSlots& slots() const { return slots_; }
+  // A state slot for work outside the schedule (scoring a sequence); -1 when every slot is taken.
+  int borrow_slot() { return slots_.take(); }
+  void return_slot(int slot) { slots_.give_back(slot); }
   const SchedulerConfig& config() const { return cfg_; }
 
  private:

@@ -277,17 +277,22 @@ class Engine:
         s.prompt_len = len(s.tokens)
         if not self.kv.can_admit(s):
             raise RuntimeError("score: sequence does not fit in the KV pool")
+        if self._has_state:                   # a state slot of its own, zeroed, for the length of the call
+            s.state_slot = self.sched.borrow_slot()
+            if s.state_slot < 0:
+                raise RuntimeError("score: every state slot is taken by a running request")
+            self.runner.pools.reset_slot(s.state_slot)
         self.kv.admit(s)
         try:
             if not self.kv.ensure(s, s.length()):
                 raise RuntimeError("score: out of cache pages")
-            if self._has_state:
-                raise RuntimeError("score: models with per-request state are scored through add_request")
             logits = self.runner.step([(s, 0, s.length(), list(range(s.length())))])
             torch.cuda.synchronize()
             K.check_errors()
         finally:
             self.kv.release(s)
+            if self._has_state:
+                self.sched.return_slot(s.state_slot)
         return logits
 
 

@@ -441,3 +441,22 @@ def test_expert_products_on_tensor_cores_against_float64(T, E, top, F, D):
         # heavy tails; the largest of some 10^5 such errors stays below 4 % of the spread, a fault is of its order
         assert (outs[-1] - ref).abs().max().item() <= 0.04 * ref.std().item(), ("tensor cores" if tensor_cores else "plain")
     assert (outs[0] - outs[1]).abs().max().item() <= 0.04 * ref.std().item()
+
+
+def test_score_borrows_a_state_slot(folders, oracle):
+    """``Engine.score`` on a model with per-request state: teacher-forced logits of a whole sequence,
+    twice (the slot is zeroed each time) and with requests running beside it."""
+    import kvcm
+    from kvcm.config import EngineConfig, KVManagerConfig, SchedulerConfig
+    name = "tlx-a"
+    B = TM.CONFIGS[name]["block_size"]
+    eng = kvcm.Engine.from_folder(folders(name, "float32"), EngineConfig(
+        kv=KVManagerConfig(num_blocks=40, block_size=B, max_seq_len=160, watermark_blocks=0),
+        sched=SchedulerConfig(max_num_seqs=3, max_batched_tokens=64), dtype="float32"))
+    toks, ref = tokens_of(name, 3), oracle(name, "float32", 3)
+    close(eng.score(toks), ref, "float32", "score")
+    eng.add_request(tokens_of(name, 2), max_new_tokens=5)
+    eng.step()
+    close(eng.score(toks), ref, "float32", "score beside a running request")
+    eng.run_until_idle()
+    assert eng.sched.slots_taken() == 0 and eng.kv.blocks_in_use(0) == 0
