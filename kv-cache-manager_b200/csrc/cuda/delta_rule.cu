@@ -13,8 +13,8 @@
 // Everything after the projections is float here, in both storage types.
 //
 // The columns of S are independent of each other, so the recurrence is spread over
-// (request, head, 32 columns) blocks; inside a block four or eight lanes share a column (rows r,
-// r + lanes, ... each) and add their partial dot products by shuffles.  The same kernel serves portions of
+// (request, head, 32 columns) blocks; inside a block four or eight lanes share a column (a run of
+// neighbouring rows each) and add their partial dot products by shuffles.  The same kernel serves portions of
 // prompts and single decoded tokens: it walks the request's rows of the step in order.  The
 // recurrence is one dependent chain per column (dot product, step, update) whose length per token
 // is what bounds a long portion of ONE request; requests and heads run side by side.
@@ -109,23 +109,35 @@ __device__ __forceinline__ void dr_copy4(float* dst, const float* src, bool ok) 
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(d), "l"(src), "r"(bytes) : "memory");
 }
 
+// 16 bytes (both addresses 16-byte aligned); `ok` false writes zeros.
+__device__ __forceinline__ void dr_copy16(float* dst, const float* src, bool ok) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
+  const int bytes = ok ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+
 // DR_LANES lanes share a column; NI: rows of S per thread (dk <= DR_LANES * NI).  TT tokens are staged
 // in shared memory at a time, in two buffers: while one tile of tokens is worked through, the next is
 // on its way (cp.async).  Eight lanes a column for the longer keys: shorter chains of dependent FMAs
 // per token and twice the warps to hide them behind.
 // DR_COLS columns of S per block: 32, or fewer where that many blocks would leave SMs idle.
-template <int DR_COLS, int DR_LANES, int NI, int TT>
+template <int DR_COLS, int DR_LANES, int NI, int TT, bool EARLY>
 __global__ void __launch_bounds__(DR_COLS * DR_LANES)
 delta_scan_kernel(const float* __restrict__ qkv, int channels, const float* __restrict__ bg,
                   float* __restrict__ state, long long state_stride, const int* __restrict__ seq_q_start,
                   const int* __restrict__ seq_q_len, const int* __restrict__ seq_state_slot,
                   float* __restrict__ out, int heads, int qk_heads, int dk, int dv) {
   constexpr int DKP = DR_LANES * NI;
-  constexpr int NIP = NI + 4;      // a lane's NI values lie together (element i = r + LANES m at [i % LANES][i / LANES]);
-                                   // the pad puts the lanes' 16-byte loads on different banks
   constexpr int CPW = 32 / DR_LANES;                      // columns per warp
-  __shared__ __align__(16) float qs[2][TT][DR_LANES][NIP];
-  __shared__ __align__(16) float ks[2][TT][DR_LANES][NIP];
+  // A token's q and k lie in shared memory as in global memory, in 16-byte pieces (so that they are
+  // staged by 16-byte copies), piece c at place c ^ (c / CH): lane r of a column owns the rows
+  // r * NI .. r * NI + NI - 1 of S, i.e. the CH = NI / 4 pieces from r * CH on, and the exclusive-or
+  // puts the pieces that the lanes of a warp read at the same time on different banks.
+  // Elements from dk on stay zero.
+  constexpr int CH = NI >= 8 ? NI / 4 : 1;
+  auto place = [](int c) { return CH >= 2 ? (c ^ ((c / CH) & 7)) : c; };
+  __shared__ __align__(16) float qs[2][TT][DKP];
+  __shared__ __align__(16) float ks[2][TT][DKP];
   __shared__ float vs[2][TT][DR_COLS];
   __shared__ float bs[2][TT], gs[2][TT];
   const int s = blockIdx.z, head = blockIdx.y;
@@ -142,28 +154,44 @@ delta_scan_kernel(const float* __restrict__ qkv, int channels, const float* __re
   float acc[NI];
 #pragma unroll
   for (int m = 0; m < NI; ++m) {
-    const int i = r + DR_LANES * m;
+    const int i = r * NI + m;
     acc[m] = (col_ok && i < dk) ? S[size_t(i) * dv] : 0.f;
   }
+  for (int idx = threadIdx.x; idx < 2 * TT * DKP; idx += blockDim.x) {
+    (&qs[0][0][0])[idx] = 0.f;
+    (&ks[0][0][0])[idx] = 0.f;
+  }
+  __syncthreads();
+  const bool vec16 = (dk % 4) == 0 && (channels % 4) == 0 && (reinterpret_cast<uintptr_t>(qkv) & 15) == 0;
   const size_t q_off = size_t(qk_head) * dk, k_off = size_t(qk_heads + qk_head) * dk;
   const size_t v_off = size_t(2 * qk_heads) * dk + size_t(head) * dv + size_t(blockIdx.x) * DR_COLS;
 
   auto stage = [&](int buf, int t0) {                   // asks for the tile of tokens t0 .. t0 + TT - 1
     const int nt = min(TT, n - t0);
-    for (int idx = threadIdx.x; idx < TT * DKP; idx += blockDim.x) {
-      const int t = idx / DKP, i = idx % DKP;
-      const bool ok = t < nt && i < dk;
-      const float* src = qkv + (ok ? size_t(q0 + t0 + t) * channels : 0);
-      dr_copy4(&qs[buf][t][i % DR_LANES][i / DR_LANES], src + (ok ? q_off + i : 0), ok);
-      dr_copy4(&ks[buf][t][i % DR_LANES][i / DR_LANES], src + (ok ? k_off + i : 0), ok);
+    if (vec16) {
+      const int per = dk / 4;
+      for (int idx = threadIdx.x; idx < TT * per; idx += blockDim.x) {
+        const int t = idx / per, c = idx % per;
+        const bool ok = t < nt;
+        const float* src = qkv + (ok ? size_t(q0 + t0 + t) * channels + 4 * c : 0);
+        dr_copy16(&qs[buf][t][4 * place(c)], src + (ok ? q_off : 0), ok);
+        dr_copy16(&ks[buf][t][4 * place(c)], src + (ok ? k_off : 0), ok);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < TT * dk; idx += blockDim.x) {
+        const int t = idx / dk, i = idx % dk;
+        const bool ok = t < nt;
+        const float* src = qkv + (ok ? size_t(q0 + t0 + t) * channels + i : 0);
+        dr_copy4(&qs[buf][t][4 * place(i / 4) + i % 4], src + (ok ? q_off : 0), ok);
+        dr_copy4(&ks[buf][t][4 * place(i / 4) + i % 4], src + (ok ? k_off : 0), ok);
+      }
     }
     for (int idx = threadIdx.x; idx < TT * DR_COLS; idx += blockDim.x) {
       const int t = idx / DR_COLS, c = idx % DR_COLS;
       const bool ok = t < nt && blockIdx.x * DR_COLS + c < dv;
       dr_copy4(&vs[buf][t][c], qkv + (ok ? size_t(q0 + t0 + t) * channels + v_off + c : 0), ok);
     }
-    if (threadIdx.x < TT) {
-      const int t = threadIdx.x;
+    for (int t = threadIdx.x; t < TT; t += blockDim.x) {
       const bool ok = t < nt;
       dr_copy4(&bs[buf][t], bg + (ok ? size_t(q0 + t0 + t) * 2 * heads + head : 0), ok);
       dr_copy4(&gs[buf][t], bg + (ok ? size_t(q0 + t0 + t) * 2 * heads + heads + head : 0), ok);
@@ -183,38 +211,68 @@ delta_scan_kernel(const float* __restrict__ qkv, int channels, const float* __re
       if constexpr (NI % 4 == 0) {
 #pragma unroll
         for (int m = 0; m < NI; m += 4) {
-          const float4 a = *reinterpret_cast<const float4*>(&ks[buf][t][r][m]);
-          const float4 b = *reinterpret_cast<const float4*>(&qs[buf][t][r][m]);
+          const int at = 4 * place((r * NI + m) / 4);
+          const float4 a = *reinterpret_cast<const float4*>(&ks[buf][t][at]);
+          const float4 b = *reinterpret_cast<const float4*>(&qs[buf][t][at]);
           kt[m] = a.x; kt[m + 1] = a.y; kt[m + 2] = a.z; kt[m + 3] = a.w;
           qt[m] = b.x; qt[m + 1] = b.y; qt[m + 2] = b.z; qt[m + 3] = b.w;
         }
       } else {
 #pragma unroll
-        for (int m = 0; m < NI; ++m) { kt[m] = ks[buf][t][r][m]; qt[m] = qs[buf][t][r][m]; }
+        for (int m = 0; m < NI; ++m) {
+          const int i = r * NI + m, at = 4 * place(i / 4) + i % 4;
+          kt[m] = ks[buf][t][at];
+          qt[m] = qs[buf][t][at];
+        }
       }
-      // four partial sums each: the chain of dependent FMAs is a quarter as long
-      float p4[4] = {0.f, 0.f, 0.f, 0.f};
+      float o;
+      if constexpr (EARLY) {
+        // Both read-outs are taken from the state BEFORE the token's write, so that neither waits for the
+        // step u:  a = S^T k,  b = S^T q,  c = k . q;  u = beta (v - g a);  o = g b + c u  (= S_new^T q).
+        // A shorter chain per token for a fifth more arithmetic: the form for few blocks.
+        float a2[2] = {0.f, 0.f}, b2[2] = {0.f, 0.f}, c2[2] = {0.f, 0.f};
 #pragma unroll
-      for (int m = 0; m < NI; ++m) p4[m & 3] = fmaf(acc[m], kt[m], p4[m & 3]);
-      float p = (p4[0] + p4[1]) + (p4[2] + p4[3]);
+        for (int m = 0; m < NI; ++m) {
+          a2[m & 1] = fmaf(acc[m], kt[m], a2[m & 1]);
+          b2[m & 1] = fmaf(acc[m], qt[m], b2[m & 1]);
+          c2[m & 1] = fmaf(kt[m], qt[m], c2[m & 1]);
+        }
+        float a = a2[0] + a2[1], b = b2[0] + b2[1], c = c2[0] + c2[1];
 #pragma unroll
-      for (int w = CPW; w < 32; w <<= 1) p += __shfl_xor_sync(0xffffffffu, p, w);
-      const float u = beta * (vs[buf][t][col_local] - g * p);
-      float o4[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int w = CPW; w < 32; w <<= 1) {
+          a += __shfl_xor_sync(0xffffffffu, a, w);
+          b += __shfl_xor_sync(0xffffffffu, b, w);
+          c += __shfl_xor_sync(0xffffffffu, c, w);
+        }
+        const float u = beta * (vs[buf][t][col_local] - g * a);
+        o = fmaf(c, u, g * b);
 #pragma unroll
-      for (int m = 0; m < NI; ++m) {
-        acc[m] = fmaf(kt[m], u, g * acc[m]);
-        o4[m & 3] = fmaf(acc[m], qt[m], o4[m & 3]);
+        for (int m = 0; m < NI; ++m) acc[m] = fmaf(kt[m], u, g * acc[m]);
+      } else {
+        // In the order of the definition; four partial sums each keep the chains of dependent FMAs short.
+        float p4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int m = 0; m < NI; ++m) p4[m & 3] = fmaf(acc[m], kt[m], p4[m & 3]);
+        float p = (p4[0] + p4[1]) + (p4[2] + p4[3]);
+#pragma unroll
+        for (int w = CPW; w < 32; w <<= 1) p += __shfl_xor_sync(0xffffffffu, p, w);
+        const float u = beta * (vs[buf][t][col_local] - g * p);
+        float o4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int m = 0; m < NI; ++m) {
+          acc[m] = fmaf(kt[m], u, g * acc[m]);
+          o4[m & 3] = fmaf(acc[m], qt[m], o4[m & 3]);
+        }
+        o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
+#pragma unroll
+        for (int w = CPW; w < 32; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
       }
-      float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
-#pragma unroll
-      for (int w = CPW; w < 32; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
       if (r == 0 && col_ok) out[size_t(q0 + t0 + t) * heads * dv + size_t(head) * dv + col] = o;
     }
   }
 #pragma unroll
   for (int m = 0; m < NI; ++m) {
-    const int i = r + DR_LANES * m;
+    const int i = r * NI + m;
     if (col_ok && i < dk) S[size_t(i) * dv] = acc[m];
   }
 }
@@ -304,9 +362,16 @@ KVCM_API int kvcm_delta_scan(const float* qkv, int channels, const float* bg, fl
   // 32 columns a block; 16 or 8 when that leaves SMs without a block (one request's long portion)
   const long long per32 = (long long)seqs * heads * ((dv + 31) / 32);
   const int cols = per32 >= sms ? 32 : (2 * per32 >= sms ? 16 : 8);
-#define KVCM_SCAN_C(COLS, LANES, NI, TT)                                                                            \
-  delta_scan_kernel<COLS, LANES, NI, TT><<<dim3((dv + COLS - 1) / COLS, heads, seqs), COLS * LANES, 0, s>>>(         \
+  // few warps for the device (one request's long portion with few heads): the form with the shorter chain
+  const bool early = per32 * 8 <= 4LL * sms;
+#define KVCM_SCAN_E(COLS, LANES, NI, TT, EARLY)                                                                     \
+  delta_scan_kernel<COLS, LANES, NI, TT, EARLY><<<dim3((dv + COLS - 1) / COLS, heads, seqs), COLS * LANES, 0, s>>>(  \
       qkv, channels, bg, state, state_stride, seq_q_start, seq_q_len, seq_state_slot, out, heads, qk_heads, dk, dv)
+#define KVCM_SCAN_C(COLS, LANES, NI, TT)                                                                            \
+  do {                                                                                                              \
+    if (early) KVCM_SCAN_E(COLS, LANES, NI, TT, true);                                                              \
+    else KVCM_SCAN_E(COLS, LANES, NI, TT, false);                                                                   \
+  } while (0)
 #define KVCM_SCAN(LANES, NI, TT)                                                                                    \
   do {                                                                                                              \
     if (cols == 32) KVCM_SCAN_C(32, LANES, NI, TT);                                                                 \
@@ -322,6 +387,7 @@ KVCM_API int kvcm_delta_scan(const float* qkv, int channels, const float* bg, fl
   else KVCM_SCAN(8, 32, 8);
 #undef KVCM_SCAN
 #undef KVCM_SCAN_C
+#undef KVCM_SCAN_E
   return KVCM_LAUNCH_RESULT();
 }
 
