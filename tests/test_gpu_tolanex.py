@@ -268,6 +268,29 @@ def test_mixers_at_the_sizes_of_the_fast_kernels(tmp_path, layer, dtype):
     close(torch.cat(outs), ref, dtype, "prompt, then single tokens")
 
 
+@pytest.mark.parametrize("heads,rank", [(2, 80), (3, 96), (2, 112), (2, 160), (1, 192), (2, 224), (20, 64), (33, 32)])
+def test_latent_ranks_and_head_counts_in_bfloat16(tmp_path, heads, rank):
+    """Every rank the tensor-core attention kernels take besides those of the other tests, and more
+    heads on the one shared latent head than a block of the decode kernel holds (16): a prompt in two
+    portions, then 24 single tokens, two requests side by side."""
+    layer = {"type": "latent_attention", "mixer": {"heads": heads, "dim": 16, "vdim": 8, "kv_rank": rank, "scale": 0.2},
+             "mlp": None}
+    folder = one_layer_model(tmp_path, layer, "bfloat16", width=64, max_positions=256)
+    a, b = helpers.random_tokens(200, 120, 31), helpers.random_tokens(150, 120, 32)
+    ra, rb = TM.plain_logits(folder, a), TM.plain_logits(folder, b)
+    r = helpers.Replayer(folder, "bfloat16", 512, 16)
+    oa = [r.step([dict(id="a", tokens=a[:100], want=list(range(100)))])]
+    both = r.step([dict(id="a", tokens=a[100:176], want=list(range(76))), dict(id="b", tokens=b[:126], want=list(range(126)))])
+    oa.append(both[:76])
+    ob = [both[76:]]
+    for k in range(24):
+        out = r.step([dict(id="a", tokens=[a[176 + k]], want=[0]), dict(id="b", tokens=[b[126 + k]], want=[0])])
+        oa.append(out[:1])
+        ob.append(out[1:])
+    close(torch.cat(oa), ra, "bfloat16", f"rank {rank}, {heads} heads, first request")
+    close(torch.cat(ob), rb, "bfloat16", f"rank {rank}, {heads} heads, second request")
+
+
 # ------------------------------------------------------------------ keys far away, at page borders
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
