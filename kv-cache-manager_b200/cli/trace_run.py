@@ -31,7 +31,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (sizes the page pool)")
     ap.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
-    ap.add_argument("--max-live", type=int, default=64, help="most requests live at a time")
+    ap.add_argument("--max-live", type=int, default=4, help="most requests live at a time (state slots)")
     ap.add_argument("--policy", default="paged", choices=["paged", "contiguous"],
                     help="cache policy (the reference's two: src/core/kv_manager.h:64-72)")
     ap.add_argument("--prefix", action="store_true",

@@ -285,3 +285,111 @@ class TolanexConfig(ModelConfig):
             d["embedding"] = {"bigram": {"buckets": self.bigram_buckets, "mul_prev": self.bigram_mul_prev,
                                          "mul_cur": self.bigram_mul_cur}}
         return d
+
+
+# ------------------------------------------------------------------------------------ Bifatar
+
+def _positive_ints(m: Dict[str, Any], keys, where: str) -> None:
+    for k in keys:
+        if _require(m, k, int, where) <= 0:
+            raise ConfigError(f"{where}: '{k}' must be positive")
+
+
+def _check_rot(m: Dict[str, Any], where: str) -> None:
+    rot = _section(m, "rot", where, optional=True)
+    if rot is None:
+        return
+    dims = _require(rot, "dims", int, where + " rot")
+    if _require(rot, "base", float, where + " rot") <= 0 or dims <= 0 or dims % 2 or dims > m["dim"]:
+        raise ConfigError(f"{where}: rot needs a positive base and an even 'dims' within 'dim', got {rot!r}")
+
+
+def _check_heads(m: Dict[str, Any], where: str) -> None:
+    _positive_ints(m, ("heads", "kv_heads", "dim", "vdim"), where)
+    if m["heads"] % m["kv_heads"]:
+        raise ConfigError(f"{where}: heads ({m['heads']}) must be a multiple of kv_heads ({m['kv_heads']})")
+
+
+@dataclass(frozen=True)
+class BifatarConfig(ModelConfig):
+    """Bifatar: a decoder whose layers are listed one by one; every layer is a parallel block
+    (one tanh norm, mixer and feed-forward read its output, their sum joins the stream).
+
+    Top level: ``vocab``, ``width``, ``norm.eps`` and ``layers``: a list of {type, mixer, mlp}.
+    ``type`` "attention": mixer {heads, kv_heads, dim, vdim, scale, rot {base, dims} (optional), mask {size}
+    (optional), softcap (optional), v_mix (optional)}; "mamba2": mixer {heads, vdim, state, groups, conv,
+    norm_groups}; "parallel": mixer {left {heads, kv_heads, dim, vdim, scale, rot (optional)}, right {heads,
+    kv_heads, dim, vdim, conv}, left_scale, right_scale}.  ``mlp`` is null or {kind: "dense", ff}.
+    ``layers`` is kept as the parsed JSON after validation; the builder reads every size from it (and the
+    ranks of the right mixer's two-stage projections from the checkpoint's shapes, see the builder)."""
+    vocab: int = 0
+    width: int = 0
+    norm_eps: float = 1e-6
+    layers: tuple = ()
+
+    @classmethod
+    def from_json_dict(cls, d: Dict[str, Any]) -> "BifatarConfig":
+        w = "config.json (Bifatar)"
+        norm = _section(d, "norm", w)
+        layers = d.get("layers")
+        if not isinstance(layers, list) or not layers:
+            raise ConfigError(f"{w}: 'layers' must be a non-empty list")
+        cfg = cls(architecture="Bifatar", vocab=_require(d, "vocab", int, w), width=_require(d, "width", int, w),
+                  norm_eps=_require(norm, "eps", float, w + " norm"), layers=tuple(json.loads(json.dumps(layers))))
+        cfg.validate()
+        return cfg
+
+    def validate(self) -> None:
+        w = "BifatarConfig"
+        if self.vocab <= 0 or self.width <= 0:
+            raise ConfigError(f"{w}: 'vocab' and 'width' must be positive")
+        if not (self.norm_eps > 0):
+            raise ConfigError(f"{w}: norm.eps must be positive, got {self.norm_eps}")
+        mixed = None
+        for i, layer in enumerate(self.layers):
+            lw = f"{w}: layer {i}"
+            if not isinstance(layer, dict):
+                raise ConfigError(f"{lw} must be an object")
+            kind = layer.get("type")
+            m = _section(layer, "mixer", lw)
+            mw = lw + " mixer"
+            if kind == "attention":
+                _check_heads(m, mw)
+                _require(m, "scale", float, mw)
+                _check_rot(m, mw)
+                mask = _section(m, "mask", mw, optional=True)
+                if mask is not None and _require(mask, "size", int, mw + " mask") <= 0:
+                    raise ConfigError(f"{mw}: mask.size must be positive")
+                if m.get("softcap") is not None and not (_require(m, "softcap", float, mw) > 0):
+                    raise ConfigError(f"{mw}: softcap must be positive")
+                if m.get("v_mix"):
+                    shape = (m["kv_heads"], m["vdim"])
+                    if mixed is not None and mixed != shape:
+                        raise ConfigError(f"{mw}: layers that mix values need the same kv_heads and vdim as the first of them")
+                    mixed = shape
+            elif kind == "mamba2":
+                _positive_ints(m, ("heads", "vdim", "state", "groups", "conv", "norm_groups"), mw)
+                if m["heads"] % m["groups"] or (m["heads"] * m["vdim"]) % m["norm_groups"]:
+                    raise ConfigError(f"{mw}: heads must be a multiple of groups and heads*vdim of norm_groups")
+            elif kind == "parallel":
+                left, right = _section(m, "left", mw), _section(m, "right", mw)
+                _check_heads(left, mw + ".left")
+                _require(left, "scale", float, mw + ".left")
+                _check_rot(left, mw + ".left")
+                _check_heads(right, mw + ".right")
+                _positive_ints(right, ("conv",), mw + ".right")
+                _require(m, "left_scale", float, mw)
+                _require(m, "right_scale", float, mw)
+            else:
+                raise ConfigError(f"{lw}: unknown type {kind!r} (known: attention, mamba2, parallel)")
+            mlp = layer.get("mlp")
+            if mlp is None:
+                continue
+            if not isinstance(mlp, dict) or mlp.get("kind") != "dense":
+                raise ConfigError(f"{lw}: mlp must be null or of kind 'dense', got {mlp!r}")
+            if _require(mlp, "ff", int, lw + " mlp") <= 0:
+                raise ConfigError(f"{lw}: mlp.ff must be positive")
+
+    def to_json_dict(self) -> Dict[str, Any]:
+        return {"architecture": self.architecture, "vocab": self.vocab, "width": self.width,
+                "norm": {"eps": self.norm_eps}, "layers": json.loads(json.dumps(list(self.layers)))}

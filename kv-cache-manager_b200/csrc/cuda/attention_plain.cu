@@ -4,6 +4,9 @@
 // With float storage this is the attention of the true 32-bit path; with bfloat16 it is the twin
 // that the fast kernels are checked against.  A row's result depends only on its own position,
 // its keys and the window, never on the batch around it.
+// Optional: scores capped as cap * tanh(score / cap); a sink per head, one more term exp(sink) in
+// the softmax's denominator that has no key and no value (the running maximum starts at the sink
+// with a sum of one and an empty accumulator).
 //
 // Arithmetic as the reference's kernel (src/cuda/paged_attention.cu:80-182): q is scaled first,
 // the causal mask is the loop bound ctx = position + 1, o = (sum_t p_t v_t) / sum_t p_t.
@@ -21,7 +24,8 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
                        const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                        const int* __restrict__ block_tables, int max_blocks,
                        const int* __restrict__ row_seq, const int* __restrict__ positions,
-                       int nh, int nkv, int hd, int block_size, float scale, int window) {
+                       int nh, int nkv, int hd, int block_size, float scale, int window, float softcap,
+                       const float* __restrict__ sink) {
   extern __shared__ float smem[];
   float* qs = smem;                     // [hd]
   float* sc = qs + hd;                  // [kPlainChunk]
@@ -38,7 +42,8 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
     qs[d] = ldf(q + size_t(row) * q_stride + size_t(h) * hd + d) * scale;
   __syncthreads();
 
-  float m = -INFINITY, l = 0.f;
+  float m = sink ? sink[h] : -INFINITY, l = sink ? 1.f : 0.f;
+  const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
   float acc[kPlainMaxDimsPerThread] = {0.f, 0.f, 0.f, 0.f};
 
   for (int c0 = lo; c0 < ctx; c0 += kPlainChunk) {
@@ -51,6 +56,7 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
                     size_t(t % block_size) * hd;
       float s = 0.f;
       for (int d = 0; d < hd; ++d) s = fmaf(qs[d], ldf(kp + d), s);
+      if (softcap > 0.f) s = softcap * tanhf(s * inv_cap);
       sc[j] = s;
       local_max = fmaxf(local_max, s);
     }
@@ -90,14 +96,14 @@ template <typename T>
 int launch_attention_plain(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
                            const void* v_cache, const int* block_tables, int max_blocks,
                            const int* row_seq, const int* positions, int rows, int nh, int nkv, int hd,
-                           int block_size, float scale, int window, cudaStream_t s) {
+                           int block_size, float scale, int window, float softcap, const float* sink, cudaStream_t s) {
   if (rows == 0) return 0;
   if (hd > kPlainMaxDimsPerThread * kPlainThreads || nkv <= 0 || nh % nkv) return KVCM_ERR_UNSUPPORTED;
   const size_t smem = (size_t(hd) + kPlainChunk + 33) * sizeof(float);
   dim3 grid(rows, nh);
   attention_plain_kernel<T><<<grid, kPlainThreads, smem, s>>>(
       (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_cache, (const T*)v_cache, block_tables,
-      max_blocks, row_seq, positions, nh, nkv, hd, block_size, scale, window);
+      max_blocks, row_seq, positions, nh, nkv, hd, block_size, scale, window, softcap, sink);
   return KVCM_LAUNCH_RESULT();
 }
 
@@ -109,17 +115,17 @@ KVCM_API int kvcm_attention_plain_f32(const void* q, int q_stride, void* out, in
                                       const void* k_cache, const void* v_cache, const int* block_tables,
                                       int max_blocks, const int* row_seq, const int* positions, int rows,
                                       int nh, int nkv, int hd, int block_size, float scale, int window,
-                                      void* stream) {
+                                      float softcap, const float* sink, void* stream) {
   return launch_attention_plain<float>(q, q_stride, out, out_stride, k_cache, v_cache, block_tables,
                                        max_blocks, row_seq, positions, rows, nh, nkv, hd, block_size,
-                                       scale, window, (cudaStream_t)stream);
+                                       scale, window, softcap, sink, (cudaStream_t)stream);
 }
 KVCM_API int kvcm_attention_plain_bf16(const void* q, int q_stride, void* out, int out_stride,
                                        const void* k_cache, const void* v_cache, const int* block_tables,
                                        int max_blocks, const int* row_seq, const int* positions, int rows,
                                        int nh, int nkv, int hd, int block_size, float scale, int window,
-                                       void* stream) {
+                                       float softcap, const float* sink, void* stream) {
   return launch_attention_plain<bf16>(q, q_stride, out, out_stride, k_cache, v_cache, block_tables,
                                       max_blocks, row_seq, positions, rows, nh, nkv, hd, block_size,
-                                      scale, window, (cudaStream_t)stream);
+                                      scale, window, softcap, sink, (cudaStream_t)stream);
 }

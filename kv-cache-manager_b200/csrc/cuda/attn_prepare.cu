@@ -1,0 +1,162 @@
+// What lies between the q|k|v product of an attention mixer and the attention kernel, for mixers
+// whose queries and keys are normalised, partly rotated or biased, and whose values may be mixed
+// with an earlier layer's.  One block per row; the row stays in shared memory as floats:
+//
+//   1. proj row [q: nh*dk | k: nkv*dk | v: nkv*dv] (float) + bias (optional)
+//   2. norm over the WHOLE q projection and over the whole k projection (optional):
+//        q <- wq * q / sqrt(mean(q^2) + eps),  k likewise with wk
+//   3. rotation of the first `rot` dimensions of every q and k head in rotate-half pairs
+//        (i, i + rot/2), angle = position * inv_freq[i]   (rot == 0: none)
+//   4. norm per head, without weights (optional):  x <- x / sqrt(mean_head(x^2) + eps)
+//   5. values: `v_keep` (optional, float [rows, nkv*dv]) receives v as projected;
+//        `v_first` (optional, the same layout) mixes:  v <- (1 - lambda) v + lambda v_first
+//   6. q goes to q_out [rows, nh*HD] in the storage type, k and v to the row's page slot
+//        [pages, nkv, page, HD]; HD >= max(dk, dv), elements beyond a head's own size are zero
+//        (zeros add nothing to a score, and the attention output's columns beyond dv stay zero).
+//
+// All arithmetic is float; the order of steps is the parameter list's, so a mixer that wants the
+// norm before the rotation uses step 2 and one that wants it after uses step 4.
+#include "common.cuh"
+#include "pdl.cuh"
+
+namespace kvcm {
+
+struct AttnPrepareParams {
+  const float* proj; int ldp;
+  const float* bias;                 // [nh*dk + nkv*dk + nkv*dv] or null
+  const float* wq; const float* wk;  // weights of the whole-projection norm, or null (no such norm)
+  const int* positions; const float* inv_freq; int rot;
+  int head_norm;                     // 1: per-head norm without weights after the rotation
+  float eps;
+  float* v_keep; const float* v_first; const float* lambda;
+  const int* slot_mapping; int block_size;
+  void* q_out; void* k_cache; void* v_cache;
+  int nh, nkv, dk, dv, HD;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+attn_prepare_kernel(AttnPrepareParams p) {
+  extern __shared__ float row[];
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  const int r = blockIdx.x, tid = threadIdx.x;
+  const int nq = p.nh * p.dk, nk = p.nkv * p.dk, nv = p.nkv * p.dv;
+  const int n = nq + nk + nv;
+  pdl_wait();
+  for (int i = tid; i < n; i += blockDim.x) {
+    float v = p.proj[size_t(r) * p.ldp + i];
+    if (p.bias) v += p.bias[i];
+    row[i] = v;
+  }
+  __syncthreads();
+  if (p.wq) {
+    float sq = 0.f, sk = 0.f;
+    for (int i = tid; i < nq; i += blockDim.x) sq = fmaf(row[i], row[i], sq);
+    for (int i = tid; i < nk; i += blockDim.x) sk = fmaf(row[nq + i], row[nq + i], sk);
+    sq = block_sum(sq, scratch);
+    sk = block_sum(sk, scratch);
+    const float iq = 1.f / sqrtf(sq / float(nq) + p.eps), ik = 1.f / sqrtf(sk / float(nk) + p.eps);
+    for (int i = tid; i < nq; i += blockDim.x) row[i] = row[i] * iq * p.wq[i];
+    for (int i = tid; i < nk; i += blockDim.x) row[nq + i] = row[nq + i] * ik * p.wk[i];
+    __syncthreads();
+  }
+  if (p.rot > 0) {
+    const int half = p.rot / 2;
+    const float pos = float(p.positions[r]);
+    const int pairs = (p.nh + p.nkv) * half;
+    for (int i = tid; i < pairs; i += blockDim.x) {
+      const int head = i / half, j = i - head * half;
+      float sn, cs;
+      sincosf(pos * p.inv_freq[j], &sn, &cs);
+      float* x = row + size_t(head) * p.dk;           // q heads, then k heads: both are dk wide and adjacent
+      float a, b;
+      rotate_pair(x[j], x[j + half], cs, sn, a, b);
+      x[j] = a;
+      x[j + half] = b;
+    }
+    __syncthreads();
+  }
+  if (p.head_norm) {
+    const int lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    for (int head = warp; head < p.nh + p.nkv; head += nwarps) {
+      float* x = row + size_t(head) * p.dk;
+      float ss = 0.f;
+      for (int i = lane; i < p.dk; i += 32) ss = fmaf(x[i], x[i], ss);
+      ss = warp_sum(ss);
+      const float inv = 1.f / sqrtf(ss / float(p.dk) + p.eps);
+      for (int i = lane; i < p.dk; i += 32) x[i] *= inv;
+    }
+    __syncthreads();
+  }
+  if (p.v_keep || p.v_first) {
+    const float lam = p.v_first ? p.lambda[0] : 0.f;
+    for (int i = tid; i < nv; i += blockDim.x) {
+      const float v = row[nq + nk + i];
+      if (p.v_keep) p.v_keep[size_t(r) * nv + i] = v;
+      if (p.v_first) row[nq + nk + i] = (1.f - lam) * v + lam * p.v_first[size_t(r) * nv + i];
+    }
+    __syncthreads();
+  }
+  T* qo = reinterpret_cast<T*>(p.q_out) + size_t(r) * p.nh * p.HD;
+  for (int i = tid; i < p.nh * p.HD; i += blockDim.x) {
+    const int head = i / p.HD, d = i - head * p.HD;
+    stf(qo + i, d < p.dk ? row[head * p.dk + d] : 0.f);
+  }
+  const int slot = p.slot_mapping ? p.slot_mapping[r] : -1;
+  if (slot < 0) return;
+  const int page = slot / p.block_size, off = slot - page * p.block_size;
+  const size_t base = (size_t(page) * p.nkv * p.block_size + off) * p.HD;
+  const size_t head_stride = size_t(p.block_size) * p.HD;
+  T* kc = reinterpret_cast<T*>(p.k_cache) + base;
+  T* vc = reinterpret_cast<T*>(p.v_cache) + base;
+  for (int i = tid; i < p.nkv * p.HD; i += blockDim.x) {
+    const int head = i / p.HD, d = i - head * p.HD;
+    stf(kc + head * head_stride + d, d < p.dk ? row[nq + head * p.dk + d] : 0.f);
+    stf(vc + head * head_stride + d, d < p.dv ? row[nq + nk + head * p.dv + d] : 0.f);
+  }
+}
+
+template <typename T>
+int launch_attn_prepare(const AttnPrepareParams& p, int rows, cudaStream_t s) {
+  if (rows == 0) return 0;
+  if (p.rot % 2 || p.rot > p.dk || p.HD < p.dk || p.HD < p.dv) return KVCM_ERR_UNSUPPORTED;
+  const size_t smem = size_t(p.nh * p.dk + p.nkv * p.dk + p.nkv * p.dv) * sizeof(float);
+  if (smem > 200 * 1024) return KVCM_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024) {
+    const cudaError_t e = cudaFuncSetAttribute(attn_prepare_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return int(e);
+  }
+  return pdl_launch(attn_prepare_kernel<T>, dim3(rows), dim3(256), smem, s, p);
+}
+
+}  // namespace kvcm
+
+using namespace kvcm;
+
+#define KVCM_ATTN_PREPARE_ARGS                                                                                        \
+  const float *proj, int ldp, const float *bias, const float *wq, const float *wk, const int *positions,              \
+      const float *inv_freq, int rot, int head_norm, float eps, float *v_keep, const float *v_first,                  \
+      const float *lambda, const int *slot_mapping, int block_size, void *q_out, void *k_cache, void *v_cache,        \
+      int rows, int nh, int nkv, int dk, int dv, int HD, void *stream
+
+static AttnPrepareParams make_params(KVCM_ATTN_PREPARE_ARGS) {
+  (void)rows; (void)stream;
+  AttnPrepareParams p;
+  p.proj = proj; p.ldp = ldp; p.bias = bias; p.wq = wq; p.wk = wk; p.positions = positions; p.inv_freq = inv_freq;
+  p.rot = inv_freq ? rot : 0; p.head_norm = head_norm; p.eps = eps; p.v_keep = v_keep; p.v_first = v_first; p.lambda = lambda;
+  p.slot_mapping = slot_mapping; p.block_size = block_size; p.q_out = q_out; p.k_cache = k_cache; p.v_cache = v_cache;
+  p.nh = nh; p.nkv = nkv; p.dk = dk; p.dv = dv; p.HD = HD;
+  return p;
+}
+
+KVCM_API int kvcm_attn_prepare_f32(KVCM_ATTN_PREPARE_ARGS) {
+  return launch_attn_prepare<float>(make_params(proj, ldp, bias, wq, wk, positions, inv_freq, rot, head_norm, eps, v_keep,
+                                                v_first, lambda, slot_mapping, block_size, q_out, k_cache, v_cache, rows, nh,
+                                                nkv, dk, dv, HD, stream), rows, (cudaStream_t)stream);
+}
+KVCM_API int kvcm_attn_prepare_bf16(KVCM_ATTN_PREPARE_ARGS) {
+  return launch_attn_prepare<bf16>(make_params(proj, ldp, bias, wq, wk, positions, inv_freq, rot, head_norm, eps, v_keep,
+                                               v_first, lambda, slot_mapping, block_size, q_out, k_cache, v_cache, rows, nh,
+                                               nkv, dk, dv, HD, stream), rows, (cudaStream_t)stream);
+}

@@ -25,14 +25,15 @@ namespace kvcm {
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
 
 // ------------------------------------------------------------------ convolution over time + SiLU
-// out[row, c] = silu( sum_j w[c, j] * in(local - (taps-1-j)) ), in(l) = this step's row l of the
+// out[row, c] = silu( bias[c] + sum_j w[c, j] * in(local - (taps-1-j)) ) (bias optional), in(l) = this step's row l of the
 // request when l >= 0, else what the state kept of earlier steps (zeros at the very start).
 template <typename T>
 __global__ void __launch_bounds__(256)
 delta_conv_kernel(const T* __restrict__ proj, int ldp, const float* __restrict__ conv_w, int taps,
                   const float* __restrict__ state, long long state_stride, long long conv_off,
                   const int* __restrict__ row_seq, const int* __restrict__ seq_q_start,
-                  const int* __restrict__ seq_state_slot, float* __restrict__ out, int channels) {
+                  const int* __restrict__ seq_state_slot, float* __restrict__ out, int channels,
+                  const float* __restrict__ bias) {
   const int row = blockIdx.x;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= channels) return;
@@ -41,7 +42,7 @@ delta_conv_kernel(const T* __restrict__ proj, int ldp, const float* __restrict__
   const int slot = seq_state_slot[s];
   const int local = row - q0;
   const float* kept = slot >= 0 ? state + slot * state_stride + conv_off : nullptr;
-  float acc = 0.f;
+  float acc = bias ? bias[c] : 0.f;
   for (int j = 0; j < taps; ++j) {
     const int l = local - (taps - 1 - j);
     float v;
@@ -121,12 +122,36 @@ __device__ __forceinline__ void dr_copy16(float* dst, const float* src, bool ok)
 // on its way (cp.async).  Eight lanes a column for the longer keys: shorter chains of dependent FMAs
 // per token and twice the warps to hide them behind.
 // DR_COLS columns of S per block: 32, or fewer where that many blocks would leave SMs idle.
-template <int DR_COLS, int DR_LANES, int NI, int TT, bool EARLY>
+//
+// MODE says which recurrence runs (the staging, the state and the split over blocks are the same):
+//   kScanDelta        S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q     one decay g per head
+//   kScanDeltaChannel the same with one decay per head AND key channel: row i of S is scaled by gd[i]
+//   kScanLinear       S <- g S + k (beta v)^T;  o = S^T q        (no correction by the state's own
+//                     read-out: the selective state-space recurrence with k = B, q = C, beta = dt, v = x)
+// Where q, k and v of a row lie is given by `q_base`, `k_base`, `v_base` (floats from the row's start).
+struct ScanArgs {
+  const float* qkv; int channels; int q_base, k_base, v_base;
+  const float* beta; int beta_ld;        // [rows, >= heads]
+  const float* g; int g_ld;              // [rows, >= heads]      (kScanDelta, kScanLinear)
+  const float* gd;                       // [rows, heads * dk]    (kScanDeltaChannel)
+  float* state; long long state_stride;
+  const int* seq_q_start; const int* seq_q_len; const int* seq_state_slot;
+  float* out; int heads, qk_heads, dk, dv;
+};
+constexpr int kScanDelta = 0, kScanDeltaChannel = 1, kScanLinear = 2;
+
+template <int DR_COLS, int DR_LANES, int NI, int TT, bool EARLY, int MODE>
 __global__ void __launch_bounds__(DR_COLS * DR_LANES)
-delta_scan_kernel(const float* __restrict__ qkv, int channels, const float* __restrict__ bg,
-                  float* __restrict__ state, long long state_stride, const int* __restrict__ seq_q_start,
-                  const int* __restrict__ seq_q_len, const int* __restrict__ seq_state_slot,
-                  float* __restrict__ out, int heads, int qk_heads, int dk, int dv) {
+delta_scan_kernel(const ScanArgs A) {
+  const float* __restrict__ qkv = A.qkv;
+  const int channels = A.channels, heads = A.heads, qk_heads = A.qk_heads, dk = A.dk, dv = A.dv;
+  float* __restrict__ state = A.state;
+  const long long state_stride = A.state_stride;
+  const int* __restrict__ seq_q_start = A.seq_q_start;
+  const int* __restrict__ seq_q_len = A.seq_q_len;
+  const int* __restrict__ seq_state_slot = A.seq_state_slot;
+  float* __restrict__ out = A.out;
+  constexpr bool CHD = MODE == kScanDeltaChannel;
   constexpr int DKP = DR_LANES * NI;
   constexpr int CPW = 32 / DR_LANES;                      // columns per warp
   // A token's q and k lie in shared memory as in global memory, in 16-byte pieces (so that they are
@@ -140,6 +165,7 @@ delta_scan_kernel(const float* __restrict__ qkv, int channels, const float* __re
   __shared__ __align__(16) float ks[2][TT][DKP];
   __shared__ float vs[2][TT][DR_COLS];
   __shared__ float bs[2][TT], gs[2][TT];
+  __shared__ __align__(16) float gds[CHD ? 2 : 1][CHD ? TT : 1][CHD ? DKP : 4];
   const int s = blockIdx.z, head = blockIdx.y;
   const int slot = seq_state_slot[s];
   if (slot < 0) return;
@@ -160,11 +186,15 @@ delta_scan_kernel(const float* __restrict__ qkv, int channels, const float* __re
   for (int idx = threadIdx.x; idx < 2 * TT * DKP; idx += blockDim.x) {
     (&qs[0][0][0])[idx] = 0.f;
     (&ks[0][0][0])[idx] = 0.f;
+    if constexpr (CHD) (&gds[0][0][0])[idx] = 1.f;
   }
   __syncthreads();
-  const bool vec16 = (dk % 4) == 0 && (channels % 4) == 0 && (reinterpret_cast<uintptr_t>(qkv) & 15) == 0;
-  const size_t q_off = size_t(qk_head) * dk, k_off = size_t(qk_heads + qk_head) * dk;
-  const size_t v_off = size_t(2 * qk_heads) * dk + size_t(head) * dv + size_t(blockIdx.x) * DR_COLS;
+  const size_t q_off = size_t(A.q_base) + size_t(qk_head) * dk, k_off = size_t(A.k_base) + size_t(qk_head) * dk;
+  const size_t v_off = size_t(A.v_base) + size_t(head) * dv + size_t(blockIdx.x) * DR_COLS;
+  const size_t gd_ld = size_t(heads) * dk, gd_off = size_t(head) * dk;
+  const bool gvec16 = CHD && (dk % 4) == 0 && (reinterpret_cast<uintptr_t>(A.gd) & 15) == 0;
+  const bool vec16 = (dk % 4) == 0 && (channels % 4) == 0 && (A.q_base % 4) == 0 && (A.k_base % 4) == 0 &&
+                     (reinterpret_cast<uintptr_t>(qkv) & 15) == 0;
 
   auto stage = [&](int buf, int t0) {                   // asks for the tile of tokens t0 .. t0 + TT - 1
     const int nt = min(TT, n - t0);
@@ -193,8 +223,24 @@ delta_scan_kernel(const float* __restrict__ qkv, int channels, const float* __re
     }
     for (int t = threadIdx.x; t < TT; t += blockDim.x) {
       const bool ok = t < nt;
-      dr_copy4(&bs[buf][t], bg + (ok ? size_t(q0 + t0 + t) * 2 * heads + head : 0), ok);
-      dr_copy4(&gs[buf][t], bg + (ok ? size_t(q0 + t0 + t) * 2 * heads + heads + head : 0), ok);
+      dr_copy4(&bs[buf][t], A.beta + (ok ? size_t(q0 + t0 + t) * A.beta_ld + head : 0), ok);
+      if constexpr (!CHD) dr_copy4(&gs[buf][t], A.g + (ok ? size_t(q0 + t0 + t) * A.g_ld + head : 0), ok);
+    }
+    if constexpr (CHD) {
+      if (gvec16) {
+        const int per = dk / 4;
+        for (int idx = threadIdx.x; idx < TT * per; idx += blockDim.x) {
+          const int t = idx / per, c = idx % per;
+          const bool ok = t < nt;
+          dr_copy16(&gds[buf][t][4 * place(c)], A.gd + (ok ? size_t(q0 + t0 + t) * gd_ld + gd_off + 4 * c : 0), ok);
+        }
+      } else {
+        for (int idx = threadIdx.x; idx < TT * dk; idx += blockDim.x) {
+          const int t = idx / dk, i = idx % dk;
+          const bool ok = t < nt;
+          dr_copy4(&gds[buf][t][4 * place(i / 4) + i % 4], A.gd + (ok ? size_t(q0 + t0 + t) * gd_ld + gd_off + i : 0), ok);
+        }
+      }
     }
     asm volatile("cp.async.commit_group;\n" ::: "memory");
   };
@@ -206,8 +252,15 @@ delta_scan_kernel(const float* __restrict__ qkv, int channels, const float* __re
     __syncthreads();                                   // this tile has landed; the other buffer has been consumed
     if (t0 + TT < n) stage(buf ^ 1, t0 + TT);
     for (int t = 0; t < nt; ++t) {
-      const float g = gs[buf][t], beta = bs[buf][t];
+      const float g = CHD ? 1.f : gs[buf][t], beta = bs[buf][t];
       float kt[NI], qt[NI];
+      if constexpr (CHD) {                            // the rows of S decay each by its own factor first
+#pragma unroll
+        for (int m = 0; m < NI; ++m) {
+          const int i = r * NI + m;
+          acc[m] *= gds[buf][t][4 * place(i / 4) + i % 4];
+        }
+      }
       if constexpr (NI % 4 == 0) {
 #pragma unroll
         for (int m = 0; m < NI; m += 4) {
@@ -250,13 +303,18 @@ delta_scan_kernel(const float* __restrict__ qkv, int channels, const float* __re
         for (int m = 0; m < NI; ++m) acc[m] = fmaf(kt[m], u, g * acc[m]);
       } else {
         // In the order of the definition; four partial sums each keep the chains of dependent FMAs short.
-        float p4[4] = {0.f, 0.f, 0.f, 0.f};
+        float u;
+        if constexpr (MODE == kScanLinear) {
+          u = beta * vs[buf][t][col_local];
+        } else {
+          float p4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int m = 0; m < NI; ++m) p4[m & 3] = fmaf(acc[m], kt[m], p4[m & 3]);
-        float p = (p4[0] + p4[1]) + (p4[2] + p4[3]);
+          for (int m = 0; m < NI; ++m) p4[m & 3] = fmaf(acc[m], kt[m], p4[m & 3]);
+          float p = (p4[0] + p4[1]) + (p4[2] + p4[3]);
 #pragma unroll
-        for (int w = CPW; w < 32; w <<= 1) p += __shfl_xor_sync(0xffffffffu, p, w);
-        const float u = beta * (vs[buf][t][col_local] - g * p);
+          for (int w = CPW; w < 32; w <<= 1) p += __shfl_xor_sync(0xffffffffu, p, w);
+          u = beta * (vs[buf][t][col_local] - g * p);
+        }
         float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int m = 0; m < NI; ++m) {
@@ -301,12 +359,13 @@ gated_rms_kernel(const float* __restrict__ o, const T* __restrict__ gate, int ld
 template <typename T>
 int launch_delta_conv(const void* proj, int ldp, const float* conv_w, int taps, float* state, long long state_stride,
                       long long conv_off, const int* row_seq, const int* seq_q_start, const int* seq_q_len,
-                      const int* seq_state_slot, float* out, int rows, int seqs, int channels, cudaStream_t s) {
+                      const int* seq_state_slot, float* out, int rows, int seqs, int channels, const float* bias,
+                      cudaStream_t s) {
   if (rows == 0) return 0;
   if (taps < 1) return KVCM_ERR_UNSUPPORTED;
   const int by = (channels + 255) / 256;
   delta_conv_kernel<T><<<dim3(rows, by), 256, 0, s>>>((const T*)proj, ldp, conv_w, taps, state, state_stride, conv_off,
-                                                      row_seq, seq_q_start, seq_state_slot, out, channels);
+                                                      row_seq, seq_q_start, seq_state_slot, out, channels, bias);
   int rc = KVCM_LAUNCH_RESULT();
   if (rc || taps == 1) return rc;
   delta_conv_state_kernel<T><<<dim3(seqs, by), 256, 0, s>>>((const T*)proj, ldp, taps, state, state_stride, conv_off,
@@ -321,16 +380,16 @@ using namespace kvcm;
 KVCM_API int kvcm_delta_conv_f32(const void* proj, int ldp, const float* conv_w, int taps, float* state,
                                  long long state_stride, long long conv_off, const int* row_seq,
                                  const int* seq_q_start, const int* seq_q_len, const int* seq_state_slot, float* out,
-                                 int rows, int seqs, int channels, void* stream) {
+                                 int rows, int seqs, int channels, const float* bias, void* stream) {
   return launch_delta_conv<float>(proj, ldp, conv_w, taps, state, state_stride, conv_off, row_seq, seq_q_start,
-                                  seq_q_len, seq_state_slot, out, rows, seqs, channels, (cudaStream_t)stream);
+                                  seq_q_len, seq_state_slot, out, rows, seqs, channels, bias, (cudaStream_t)stream);
 }
 KVCM_API int kvcm_delta_conv_bf16(const void* proj, int ldp, const float* conv_w, int taps, float* state,
                                   long long state_stride, long long conv_off, const int* row_seq,
                                   const int* seq_q_start, const int* seq_q_len, const int* seq_state_slot, float* out,
-                                  int rows, int seqs, int channels, void* stream) {
+                                  int rows, int seqs, int channels, const float* bias, void* stream) {
   return launch_delta_conv<bf16>(proj, ldp, conv_w, taps, state, state_stride, conv_off, row_seq, seq_q_start,
-                                 seq_q_len, seq_state_slot, out, rows, seqs, channels, (cudaStream_t)stream);
+                                 seq_q_len, seq_state_slot, out, rows, seqs, channels, bias, (cudaStream_t)stream);
 }
 
 KVCM_API int kvcm_delta_prepare(float* qkv, int channels, float* ba, const float* a_log, const float* dt_bias,
@@ -347,12 +406,9 @@ KVCM_API int kvcm_delta_scan_max_dk() { return 256; }
 // `rows`: rows of the step.  When every request brings one row (rows == seqs) the kernel is bound by
 // reading and writing the state: four lanes a column then, so that a warp's access covers whole
 // 32-byte sectors of a row of S.
-KVCM_API int kvcm_delta_scan(const float* qkv, int channels, const float* bg, float* state, long long state_stride,
-                             const int* seq_q_start, const int* seq_q_len, const int* seq_state_slot, float* out,
-                             int rows, int seqs, int heads, int qk_heads, int dk, int dv, void* stream) {
-  if (seqs == 0) return 0;
-  if (dk < 1 || dk > 256 || qk_heads < 1 || heads % qk_heads) return KVCM_ERR_UNSUPPORTED;
-  cudaStream_t s = (cudaStream_t)stream;
+template <int MODE>
+static int launch_scan(const ScanArgs& A, int rows, int seqs, cudaStream_t s) {
+  const int heads = A.heads, dk = A.dk, dv = A.dv;
   static int sms = 0;
   if (sms == 0) {
     int dev = 0;
@@ -363,13 +419,16 @@ KVCM_API int kvcm_delta_scan(const float* qkv, int channels, const float* bg, fl
   const long long per32 = (long long)seqs * heads * ((dv + 31) / 32);
   const int cols = per32 >= sms ? 32 : (2 * per32 >= sms ? 16 : 8);
   // few warps for the device (one request's long portion with few heads): the form with the shorter chain
-  const bool early = per32 * 8 <= 4LL * sms;
+  // (it has no meaning for the linear recurrence, whose step does not read the state)
+  const bool early = MODE != kScanLinear && per32 * 8 <= 4LL * sms;
+  // with a decay per channel a third staged array shares the static shared memory: fewer tokens a tile
+  constexpr int TT_LONG = MODE == kScanDeltaChannel ? 8 : 16, TT_LONGEST = MODE == kScanDeltaChannel ? 4 : 8;
 #define KVCM_SCAN_E(COLS, LANES, NI, TT, EARLY)                                                                     \
-  delta_scan_kernel<COLS, LANES, NI, TT, EARLY><<<dim3((dv + COLS - 1) / COLS, heads, seqs), COLS * LANES, 0, s>>>(  \
-      qkv, channels, bg, state, state_stride, seq_q_start, seq_q_len, seq_state_slot, out, heads, qk_heads, dk, dv)
+  delta_scan_kernel<COLS, LANES, NI, TT, EARLY, MODE><<<dim3((dv + COLS - 1) / COLS, heads, seqs), COLS * LANES, 0, s>>>(A)
 #define KVCM_SCAN_C(COLS, LANES, NI, TT)                                                                            \
   do {                                                                                                              \
-    if (early) KVCM_SCAN_E(COLS, LANES, NI, TT, true);                                                              \
+    if constexpr (MODE == kScanLinear) KVCM_SCAN_E(COLS, LANES, NI, TT, false);                                     \
+    else if (early) KVCM_SCAN_E(COLS, LANES, NI, TT, true);                                                         \
     else KVCM_SCAN_E(COLS, LANES, NI, TT, false);                                                                   \
   } while (0)
 #define KVCM_SCAN(LANES, NI, TT)                                                                                    \
@@ -383,11 +442,185 @@ KVCM_API int kvcm_delta_scan(const float* qkv, int channels, const float* bg, fl
   else if (dk <= 16) KVCM_SCAN(4, 4, 16);
   else if (dk <= 32) KVCM_SCAN(4, 8, 16);
   else if (dk <= 64) { if (single_rows) KVCM_SCAN(4, 16, 16); else KVCM_SCAN(8, 8, 16); }
-  else if (dk <= 128) { if (single_rows) KVCM_SCAN(4, 32, 16); else KVCM_SCAN(8, 16, 16); }
-  else KVCM_SCAN(8, 32, 8);
+  else if (dk <= 128) { if (single_rows) KVCM_SCAN(4, 32, TT_LONG); else KVCM_SCAN(8, 16, TT_LONG); }
+  else KVCM_SCAN(8, 32, TT_LONGEST);
 #undef KVCM_SCAN
 #undef KVCM_SCAN_C
 #undef KVCM_SCAN_E
+  return KVCM_LAUNCH_RESULT();
+}
+
+// mode: 0 delta rule with one decay per head (g), 1 delta rule with a decay per head and key channel (gd),
+// 2 linear recurrence (see the kernel).  The row layout of `qkv` is given by the three bases.
+KVCM_API int kvcm_state_scan(int mode, const float* qkv, int channels, int q_base, int k_base, int v_base,
+                             const float* beta, int beta_ld, const float* g, int g_ld, const float* gd, float* state,
+                             long long state_stride, const int* seq_q_start, const int* seq_q_len,
+                             const int* seq_state_slot, float* out, int rows, int seqs, int heads, int qk_heads, int dk,
+                             int dv, void* stream) {
+  if (seqs == 0) return 0;
+  if (dk < 1 || dk > 256 || qk_heads < 1 || heads % qk_heads) return KVCM_ERR_UNSUPPORTED;
+  if ((mode == kScanDeltaChannel) != (gd != nullptr) || (mode != kScanDeltaChannel && !g) || !beta) return KVCM_ERR_UNSUPPORTED;
+  ScanArgs A;
+  A.qkv = qkv; A.channels = channels; A.q_base = q_base; A.k_base = k_base; A.v_base = v_base;
+  A.beta = beta; A.beta_ld = beta_ld; A.g = g; A.g_ld = g_ld; A.gd = gd; A.state = state; A.state_stride = state_stride;
+  A.seq_q_start = seq_q_start; A.seq_q_len = seq_q_len; A.seq_state_slot = seq_state_slot; A.out = out;
+  A.heads = heads; A.qk_heads = qk_heads; A.dk = dk; A.dv = dv;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (mode == kScanDelta) return launch_scan<kScanDelta>(A, rows, seqs, s);
+  if (mode == kScanDeltaChannel) return launch_scan<kScanDeltaChannel>(A, rows, seqs, s);
+  if (mode == kScanLinear) return launch_scan<kScanLinear>(A, rows, seqs, s);
+  return KVCM_ERR_UNSUPPORTED;
+}
+
+// The delta rule with one decay per head: rows of `qkv` are [q | k | v], `bg` rows are [beta | g].
+KVCM_API int kvcm_delta_scan(const float* qkv, int channels, const float* bg, float* state, long long state_stride,
+                             const int* seq_q_start, const int* seq_q_len, const int* seq_state_slot, float* out,
+                             int rows, int seqs, int heads, int qk_heads, int dk, int dv, void* stream) {
+  return kvcm_state_scan(kScanDelta, qkv, channels, 0, qk_heads * dk, 2 * qk_heads * dk, bg, 2 * heads, bg + heads, 2 * heads,
+                         nullptr, state, state_stride, seq_q_start, seq_q_len, seq_state_slot, out, rows, seqs, heads,
+                         qk_heads, dk, dv, stream);
+}
+
+// ---------------------------------------------------- what the other recurrent mixers need around the scan
+
+// Unit vectors as in delta_prepare; beta[row, h] = sigmoid(b[row, h]) (b in the storage type, row stride ldb);
+// a[row, h, i] (float, in place) becomes the decay exp(-exp(A_log[h]) softplus(a + dt_bias[h, i])).
+template <typename T>
+__global__ void __launch_bounds__(128)
+delta_prepare_channel_kernel(float* __restrict__ qkv, int channels, const T* __restrict__ b, int ldb,
+                             float* __restrict__ beta, float* __restrict__ a, const float* __restrict__ a_log,
+                             const float* __restrict__ dt_bias, int heads, int qk_heads, int dk) {
+  const int row = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const float qscale = 1.f / sqrtf(float(dk));
+  for (int hh = warp; hh < 2 * qk_heads; hh += nwarps) {
+    float* p = qkv + size_t(row) * channels + size_t(hh) * dk;
+    float ss = 0.f;
+    for (int i = lane; i < dk; i += 32) ss += p[i] * p[i];
+    ss = warp_sum(ss);
+    float inv = 1.f / sqrtf(ss + 1e-6f);
+    if (hh < qk_heads) inv *= qscale;
+    for (int i = lane; i < dk; i += 32) p[i] *= inv;
+  }
+  for (int h = threadIdx.x; h < heads; h += blockDim.x)
+    beta[size_t(row) * heads + h] = 1.f / (1.f + expf(-ldf(b + size_t(row) * ldb + h)));
+  for (int i = threadIdx.x; i < heads * dk; i += blockDim.x) {
+    const float z = a[size_t(row) * heads * dk + i] + dt_bias[i];
+    const float sp = z > 20.f ? z : log1pf(expf(z));
+    a[size_t(row) * heads * dk + i] = expf(-expf(a_log[i / dk]) * sp);
+  }
+}
+
+// Step sizes and decays of the selective state-space recurrence: dt = softplus(raw + dt_bias) (no clamp),
+// decay = exp(-exp(A_log) dt); out rows are [dt | decay].
+template <typename T>
+__global__ void __launch_bounds__(128)
+ssm_prepare_kernel(const T* __restrict__ raw, int ld, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                   float* __restrict__ out, int rows, int heads) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * heads) return;
+  const int row = idx / heads, h = idx - row * heads;
+  const float z = ldf(raw + size_t(row) * ld + h) + dt_bias[h];
+  const float dt = z > 20.f ? z : log1pf(expf(z));
+  out[size_t(row) * 2 * heads + h] = dt;
+  out[size_t(row) * 2 * heads + heads + h] = expf(-expf(a_log[h]) * dt);
+}
+
+// Norm of the recurrent mixers' outputs in groups of `group` neighbouring elements, with a gate:
+//   v_i   = (o_i + skip_coef[i / head] * skip_i)  [* act(z_i) when the gate comes BEFORE the norm]
+//   out_i = storage( v_i / sqrt(mean_group(v^2) + eps) * w[i % wlen]  [* act(z_i) when it comes after] )
+// act: 0 = SiLU, 1 = sigmoid.  o float [rows, n]; z storage type (row stride ldz); skip float (row stride lds,
+// optional, with one coefficient per `head` elements).  One warp per (row, group).
+__device__ __forceinline__ float gate_act(float z, int act) {
+  const float sg = 1.f / (1.f + expf(-z));
+  return act == 0 ? z * sg : sg;
+}
+template <typename T>
+__global__ void __launch_bounds__(128)
+group_rms_gate_kernel(const float* __restrict__ o, const T* __restrict__ z, int ldz, const float* __restrict__ skip, int lds,
+                      const float* __restrict__ skip_coef, int head, const float* __restrict__ w, int wlen,
+                      T* __restrict__ out, int n, int group, int gate_first, int act, float eps) {
+  const int row = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int groups = n / group;
+  for (int g = blockIdx.y * nwarps + warp; g < groups; g += gridDim.y * nwarps) {
+    const int i0 = g * group;
+    float ss = 0.f;
+    for (int j = lane; j < group; j += 32) {
+      const int i = i0 + j;
+      float v = o[size_t(row) * n + i];
+      if (skip) v = fmaf(skip_coef[i / head], skip[size_t(row) * lds + i], v);
+      if (gate_first) v *= gate_act(ldf(z + size_t(row) * ldz + i), act);
+      ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.f / sqrtf(ss / float(group) + eps);
+    for (int j = lane; j < group; j += 32) {
+      const int i = i0 + j;
+      float v = o[size_t(row) * n + i];
+      if (skip) v = fmaf(skip_coef[i / head], skip[size_t(row) * lds + i], v);
+      const float gz = gate_act(ldf(z + size_t(row) * ldz + i), act);
+      if (gate_first) v *= gz;
+      v = v * inv * w[i % wlen];
+      if (!gate_first) v *= gz;
+      stf(out + size_t(row) * n + i, v);
+    }
+  }
+}
+
+template <typename T>
+static int launch_group_rms_gate(const float* o, const void* z, int ldz, const float* skip, int lds, const float* skip_coef,
+                                 int head, const float* w, int wlen, void* out, int rows, int n, int group, int gate_first,
+                                 int act, float eps, cudaStream_t s) {
+  if (rows == 0) return 0;
+  if (group < 1 || n % group || wlen < 1 || (skip && head < 1)) return KVCM_ERR_UNSUPPORTED;
+  const int groups = n / group;
+  group_rms_gate_kernel<T><<<dim3(rows, (groups + 3) / 4), 128, 0, s>>>(o, (const T*)z, ldz, skip, lds, skip_coef, head, w, wlen,
+                                                                       (T*)out, n, group, gate_first, act, eps);
+  return KVCM_LAUNCH_RESULT();
+}
+
+#define KVCM_GROUP_RMS_ARGS                                                                                          \
+  const float *o, const void *z, int ldz, const float *skip, int lds, const float *skip_coef, int head, const float *w, \
+      int wlen, void *out, int rows, int n, int group, int gate_first, int act, float eps, void *stream
+KVCM_API int kvcm_group_rms_gate_f32(KVCM_GROUP_RMS_ARGS) {
+  return launch_group_rms_gate<float>(o, z, ldz, skip, lds, skip_coef, head, w, wlen, out, rows, n, group, gate_first, act, eps,
+                                      (cudaStream_t)stream);
+}
+KVCM_API int kvcm_group_rms_gate_bf16(KVCM_GROUP_RMS_ARGS) {
+  return launch_group_rms_gate<bf16>(o, z, ldz, skip, lds, skip_coef, head, w, wlen, out, rows, n, group, gate_first, act, eps,
+                                     (cudaStream_t)stream);
+}
+
+KVCM_API int kvcm_delta_prepare_channel_f32(float* qkv, int channels, const void* b, int ldb, float* beta, float* a,
+                                            const float* a_log, const float* dt_bias, int rows, int heads, int qk_heads,
+                                            int dk, void* stream) {
+  if (rows == 0) return 0;
+  delta_prepare_channel_kernel<float><<<rows, 128, 0, (cudaStream_t)stream>>>(qkv, channels, (const float*)b, ldb, beta, a,
+                                                                              a_log, dt_bias, heads, qk_heads, dk);
+  return KVCM_LAUNCH_RESULT();
+}
+KVCM_API int kvcm_delta_prepare_channel_bf16(float* qkv, int channels, const void* b, int ldb, float* beta, float* a,
+                                             const float* a_log, const float* dt_bias, int rows, int heads, int qk_heads,
+                                             int dk, void* stream) {
+  if (rows == 0) return 0;
+  delta_prepare_channel_kernel<bf16><<<rows, 128, 0, (cudaStream_t)stream>>>(qkv, channels, (const bf16*)b, ldb, beta, a,
+                                                                             a_log, dt_bias, heads, qk_heads, dk);
+  return KVCM_LAUNCH_RESULT();
+}
+
+KVCM_API int kvcm_ssm_prepare_f32(const void* raw, int ld, const float* a_log, const float* dt_bias, float* out, int rows,
+                                  int heads, void* stream) {
+  if (rows == 0) return 0;
+  ssm_prepare_kernel<float><<<(rows * heads + 127) / 128, 128, 0, (cudaStream_t)stream>>>((const float*)raw, ld, a_log, dt_bias,
+                                                                                         out, rows, heads);
+  return KVCM_LAUNCH_RESULT();
+}
+KVCM_API int kvcm_ssm_prepare_bf16(const void* raw, int ld, const float* a_log, const float* dt_bias, float* out, int rows,
+                                   int heads, void* stream) {
+  if (rows == 0) return 0;
+  ssm_prepare_kernel<bf16><<<(rows * heads + 127) / 128, 128, 0, (cudaStream_t)stream>>>((const bf16*)raw, ld, a_log, dt_bias,
+                                                                                        out, rows, heads);
   return KVCM_LAUNCH_RESULT();
 }
 

@@ -36,9 +36,9 @@ int kvcm_silu_mul_f32(const void*, void*, int, int, void*);
 int kvcm_silu_mul_bf16(const void*, void*, int, int, void*);
 int kvcm_gemm_plain_f32(const void*, const void*, void*, int, int, int, int, int, int, void*);
 int kvcm_attention_plain_f32(const void*, int, void*, int, const void*, const void*, const int*, int, const int*, const int*,
-                             int, int, int, int, int, float, int, void*);
+                             int, int, int, int, int, float, int, float, const float*, void*);
 int kvcm_attention_plain_bf16(const void*, int, void*, int, const void*, const void*, const int*, int, const int*, const int*,
-                              int, int, int, int, int, float, int, void*);
+                              int, int, int, int, int, float, int, float, const float*, void*);
 int kvcm_attention_fast_supports(int);
 int kvcm_attention_decode_resident_blocks(int);
 int kvcm_attention_decode_cluster_parts(void);
@@ -160,7 +160,7 @@ int attention(const KvcmForwardArgs& a, const KvcmForwardLayer& L, const void* q
     ++launches;
     return (a.f32 ? kvcm_attention_plain_f32 : kvcm_attention_plain_bf16)(
         q, q_stride, a.attn, a.nh * a.hd, L.k_cache, L.v_cache, tables, a.max_blocks, a.row_seq, a.positions, a.rows, a.nh,
-        a.nkv, a.hd, a.block_size, a.scale, L.window, s);
+        a.nkv, a.hd, a.block_size, a.scale, L.window, 0.f, nullptr, s);
   }
   int rc = 0;
   const int nd = a.decode_seqs;

@@ -286,10 +286,15 @@ def gemm_plain(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
 
 def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     block_tables: torch.Tensor, row_seq: torch.Tensor, positions: torch.Tensor,
-                    nh: int, nkv: int, hd: int, scale: float, window: int = 0) -> None:
+                    nh: int, nkv: int, hd: int, scale: float, window: int = 0, softcap: float = 0.0,
+                    sink: Optional[torch.Tensor] = None) -> None:
     """Row-per-query paged attention.  q: [T, >= nh*hd] (row stride free), out: [T, nh*hd];
-    caches [pages, nkv, block, hd]; block_tables int32 [S, max_blocks]."""
-    _cuda(q, out, k_cache, v_cache, block_tables, row_seq, positions)
+    caches [pages, nkv, block, hd]; block_tables int32 [S, max_blocks].  ``softcap`` > 0 caps the
+    scaled scores as cap * tanh(score / cap); ``sink`` (float32 [nh]) adds exp(sink) of each head to
+    its softmax denominators."""
+    _cuda(q, out, k_cache, v_cache, block_tables, row_seq, positions, sink)
+    _need(sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == nh),
+          "attention: sink float32 [heads]")
     T = out.shape[0]
     _need(q.stride(1) == 1 and out.stride(1) == 1, "attention: rows must be dense")
     _need(q.dtype == out.dtype == k_cache.dtype == v_cache.dtype, "attention: dtypes differ")
@@ -302,7 +307,8 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
     fn = getattr(_lib(), "kvcm_attention_plain_" + _suffix(q))
     _check(fn(_p(q), q.stride(0), _p(out), out.stride(0), _p(k_cache), _p(v_cache), _p(block_tables),
               block_tables.shape[1], _p(row_seq), _p(positions), T, nh, nkv, hd, k_cache.shape[2],
-              ctypes.c_float(scale), int(window), _stream()), "attention_plain", f"(hd={hd}, nh={nh}, nkv={nkv})")
+              ctypes.c_float(scale), int(window), ctypes.c_float(softcap), _p(sink), _stream()), "attention_plain",
+           f"(hd={hd}, nh={nh}, nkv={nkv})")
 
 
 # Kernel families whose bounded waits report through an error word, in the order of the status
@@ -384,14 +390,15 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, seed: torch.Tensor,
 
 def paged_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     block_tables: torch.Tensor, ctx, nh: int, nkv: int, hd: int, scale: float,
-                    window: int = 0) -> None:
+                    window: int = 0, softcap: float = 0.0, sink: Optional[torch.Tensor] = None) -> None:
     """Attention of all rows of a step.  Rows [0, ctx.decode_seqs) are single-row entries, the
     rest are the rows of longer portions.  ``ctx.options['attention']``: 'plain' forces the plain
     kernel for every row; float32 storage always uses it (the true 32-bit path)."""
     mode = ctx.options.get("attention", "auto")
-    if mode == "plain" or q.dtype == torch.float32 or not fast_attention_supported(nh, nkv, hd, k_cache.shape[2]):
+    if mode == "plain" or q.dtype == torch.float32 or not fast_attention_supported(nh, nkv, hd, k_cache.shape[2]) \
+            or softcap > 0.0 or sink is not None:
         attention_plain(q, out, k_cache, v_cache, block_tables, ctx.row_seq, ctx.positions,
-                        nh, nkv, hd, scale, window)
+                        nh, nkv, hd, scale, window, softcap, sink)
         return
     nd = ctx.decode_seqs
     if nd > 0:
@@ -937,19 +944,20 @@ def delta_scan_max_dk() -> int:
 
 
 def delta_conv(proj: torch.Tensor, conv_w: torch.Tensor, state: torch.Tensor, conv_off: int, ctx,
-               out: torch.Tensor) -> None:
+               out: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
     """Causal convolution over time + SiLU of the first ``channels`` columns of ``proj`` into float32
     ``out`` [T, channels]; earlier inputs come from (and the newest go to) the requests' state rows."""
-    _cuda(proj, conv_w, state, out)
+    _cuda(proj, conv_w, state, out, bias)
     T, C = out.shape
     taps = conv_w.shape[1]
+    _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == C), "delta_conv: bias float32 [channels]")
     _need(conv_w.dtype == torch.float32 and conv_w.is_contiguous() and conv_w.shape[0] == C, "delta_conv: taps [channels, taps] float32")
     _need(out.dtype == torch.float32 and out.is_contiguous() and proj.stride(1) == 1 and proj.shape[1] >= C, "delta_conv: layout")
     _need(state.dtype == torch.float32 and state.is_contiguous() and state.dim() == 2
           and state.shape[1] >= conv_off + (taps - 1) * C, "delta_conv: state rows too short")
     fn = getattr(_lib(), "kvcm_delta_conv_" + _suffix(proj))
     _check(fn(_p(proj), proj.stride(0), _p(conv_w), taps, _p(state), _ll(state.stride(0)), _ll(conv_off), _p(ctx.row_seq),
-              _p(ctx.seq_q_start), _p(ctx.seq_q_len), _p(ctx.seq_state_slot), _p(out), T, ctx.seqs, C, _stream()), "delta_conv")
+              _p(ctx.seq_q_start), _p(ctx.seq_q_len), _p(ctx.seq_state_slot), _p(out), T, ctx.seqs, C, _p(bias), _stream()), "delta_conv")
     if taps > 1:
         global _launches
         _launches += 1                      # the state update
@@ -1084,3 +1092,146 @@ def moe_combine(y: torch.Tensor, work: torch.Tensor, wt: torch.Tensor, experts: 
     _need(y.shape == (T * top, D) and (shared_y is None or shared_y.shape == (T, D)) and work.dtype == _I32, "moe_combine: shapes")
     _check(_lib().kvcm_moe_combine(_p(y), _p(work), _p(wt), top, int(experts), _p(shared_y), _p(gate), _p(out), T, D,
                                    _stream()), "moe_combine")
+
+
+# ------------------------------------------------- recurrences beside the head-wise delta rule
+
+SCAN_DELTA, SCAN_DELTA_CHANNEL, SCAN_LINEAR = 0, 1, 2
+
+
+def state_scan(mode: int, qkv: torch.Tensor, bases, beta: torch.Tensor, g: Optional[torch.Tensor],
+               gd: Optional[torch.Tensor], state: torch.Tensor, ctx, out: torch.Tensor, heads: int, qk_heads: int,
+               dk: int, dv: int) -> None:
+    """The matrix-state recurrences over every request's rows of the step, from and into its state row
+    (csrc/cuda/delta_rule.cu).  ``bases`` = where a row's q, k and v start; ``beta`` [T, >= heads] (a view
+    with a row stride is fine), ``g`` likewise (one decay per head) or ``gd`` [T, heads*dk] (one per head
+    and key channel)."""
+    _cuda(qkv, beta, g, gd, state, out)
+    _need(all(t is None or t.dtype == torch.float32 for t in (qkv, beta, g, gd, state, out)), "state_scan: float32")
+    _need(qkv.is_contiguous() and out.is_contiguous() and state.is_contiguous() and beta.stride(1) == 1
+          and (g is None or g.stride(1) == 1) and (gd is None or (gd.is_contiguous() and gd.shape == (qkv.shape[0], heads * dk))),
+          "state_scan: layout")
+    qb, kb, vb = (int(b) for b in bases)
+    C = qkv.shape[1]
+    _need(max(qb, kb) + qk_heads * dk <= C and vb + heads * dv <= C and out.shape == (qkv.shape[0], heads * dv)
+          and state.shape[1] >= heads * dk * dv and beta.shape[1] >= heads, "state_scan: shapes")
+    _check(_lib().kvcm_state_scan(int(mode), _p(qkv), C, qb, kb, vb, _p(beta), beta.stride(0), _p(g),
+                                  g.stride(0) if g is not None else 0, _p(gd), _p(state), _ll(state.stride(0)),
+                                  _p(ctx.seq_q_start), _p(ctx.seq_q_len), _p(ctx.seq_state_slot), _p(out), qkv.shape[0],
+                                  ctx.seqs, heads, qk_heads, dk, dv, _stream()), "state_scan", f"(mode={mode}, dk={dk}, dv={dv})")
+
+
+def delta_prepare_channel(qkv: torch.Tensor, b: torch.Tensor, beta: torch.Tensor, a: torch.Tensor, a_log: torch.Tensor,
+                          dt_bias: torch.Tensor, heads: int, qk_heads: int, dk: int) -> None:
+    """In place: query and key heads of ``qkv`` to unit length (queries also times dk^-1/2); ``beta`` =
+    sigmoid(b) (b [T, heads] in the storage dtype, any row stride); ``a`` [T, heads*dk] float32 becomes the
+    decays exp(-exp(A_log[head]) softplus(a + dt_bias))."""
+    _cuda(qkv, b, beta, a, a_log, dt_bias)
+    T = qkv.shape[0]
+    _need(all(t.dtype == torch.float32 and t.is_contiguous() for t in (qkv, beta, a, a_log, dt_bias)), "delta_prepare_channel: float32")
+    _need(b.stride(1) == 1 and b.shape == (T, heads) and beta.shape == (T, heads) and a.shape == (T, heads * dk)
+          and a_log.numel() == heads and dt_bias.numel() == heads * dk and qkv.shape[1] >= 2 * qk_heads * dk,
+          "delta_prepare_channel: shapes")
+    fn = getattr(_lib(), "kvcm_delta_prepare_channel_" + _suffix(b))
+    _check(fn(_p(qkv), qkv.shape[1], _p(b), b.stride(0), _p(beta), _p(a), _p(a_log), _p(dt_bias), T, heads, qk_heads, dk,
+              _stream()), "delta_prepare_channel")
+
+
+def ssm_prepare(raw: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, out: torch.Tensor, heads: int) -> None:
+    """out [T, 2*heads] float32 = [softplus(raw + dt_bias) | exp(-exp(A_log) * that)]; raw [T, heads] storage dtype."""
+    _cuda(raw, a_log, dt_bias, out)
+    T = raw.shape[0]
+    _need(raw.stride(1) == 1 and raw.shape[1] == heads and out.dtype == torch.float32 and out.is_contiguous()
+          and out.shape == (T, 2 * heads) and a_log.dtype == torch.float32 and dt_bias.dtype == torch.float32
+          and a_log.numel() == heads and dt_bias.numel() == heads, "ssm_prepare: layout")
+    fn = getattr(_lib(), "kvcm_ssm_prepare_" + _suffix(raw))
+    _check(fn(_p(raw), raw.stride(0), _p(a_log), _p(dt_bias), _p(out), T, heads, _stream()), "ssm_prepare")
+
+
+def group_rms_gate(o: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, group: int, eps: float,
+                   gate_first: bool, act: str, skip: Optional[torch.Tensor] = None,
+                   skip_coef: Optional[torch.Tensor] = None, head: int = 1) -> None:
+    """Norm in groups of ``group`` neighbouring elements with a gate ``act`` ('silu' | 'sigmoid') of z before or
+    after it; ``weight`` is indexed modulo its length; optional skip term ``skip_coef[i // head] * skip[:, i]``
+    added to o first.  o/skip float32, z/out storage dtype (z and skip may have a row stride)."""
+    _cuda(o, z, weight, out, skip, skip_coef)
+    T, n = o.shape
+    _need(o.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous() and out.shape == o.shape
+          and z.stride(1) == 1 and z.shape[1] >= n and z.dtype == out.dtype and weight.dtype == torch.float32
+          and weight.is_contiguous() and n % group == 0, "group_rms_gate: layout")
+    _need((skip is None) == (skip_coef is None), "group_rms_gate: skip and its coefficients come together")
+    if skip is not None:
+        _need(skip.dtype == torch.float32 and skip.stride(1) == 1 and skip.shape[1] >= n and skip_coef.dtype == torch.float32
+              and skip_coef.is_contiguous() and skip_coef.numel() * head >= n, "group_rms_gate: skip layout")
+    fn = getattr(_lib(), "kvcm_group_rms_gate_" + _suffix(out))
+    _check(fn(_p(o), _p(z), z.stride(0), _p(skip), skip.stride(0) if skip is not None else 0, _p(skip_coef), int(head),
+              _p(weight), weight.numel(), _p(out), T, n, int(group), int(bool(gate_first)), {"silu": 0, "sigmoid": 1}[act],
+              ctypes.c_float(eps), _stream()), "group_rms_gate")
+
+
+# ------------------------------------------------------- blocks with one norm and summed sublayers
+
+def dyt_norm(x: torch.Tensor, pending, weight: torch.Tensor, bias: torch.Tensor, alpha: torch.Tensor,
+             out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    """x += sum of scale * tensor over ``pending`` (up to three (float32 tensor, scale) pairs; with ``rows``
+    the sum is formed for the gathered rows only and x is left alone), then
+    out = tanh(alpha * x) * weight + bias.  weight/bias float32 [H], alpha float32 [1] on the device."""
+    pend = list(pending or [])
+    _need(len(pend) <= 3, "dyt_norm: at most three pending outputs")
+    _cuda(x, weight, bias, alpha, out, rows, *[t for t, _ in pend])
+    H = x.shape[1]
+    n = out.shape[0]
+    _need(x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and out.shape[1] == H, "dyt_norm: x float32 [T,H]")
+    _need(all(t.dtype == torch.float32 and t.is_contiguous() and t.numel() >= H for t in (weight, bias))
+          and alpha.dtype == torch.float32 and alpha.numel() == 1, "dyt_norm: weight/bias/alpha float32")
+    for t, _ in pend:
+        _need(t.dtype == torch.float32 and t.is_contiguous() and t.shape == x.shape, "dyt_norm: pending float32 like x")
+    if rows is None:
+        _need(n == x.shape[0], "dyt_norm: out rows != x rows")
+    else:
+        _need(rows.dtype == _I32 and rows.numel() >= n, "dyt_norm: rows int32 [n]")
+    pend += [(None, 0.0)] * (3 - len(pend))
+    fn = getattr(_lib(), "kvcm_dyt_norm_" + _suffix(out))
+    _check(fn(_p(x), _p(pend[0][0]), ctypes.c_float(pend[0][1]), _p(pend[1][0]), ctypes.c_float(pend[1][1]),
+              _p(pend[2][0]), ctypes.c_float(pend[2][1]), _p(weight), _p(bias), _p(alpha), _p(out), _p(rows), n, H,
+              _stream()), "dyt_norm")
+
+
+def relu_sq(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = max(x, 0)^2, elementwise, in the storage dtype."""
+    _cuda(x, out)
+    _need(x.is_contiguous() and out.is_contiguous() and x.shape == out.shape and x.dtype == out.dtype, "relu_sq: layout")
+    fn = getattr(_lib(), "kvcm_relu_sq_" + _suffix(x))
+    _check(fn(_p(x), _p(out), _ll(x.numel()), _stream()), "relu_sq")
+
+
+def attn_prepare(proj: torch.Tensor, bias: Optional[torch.Tensor], wq: Optional[torch.Tensor], wk: Optional[torch.Tensor],
+                 positions: torch.Tensor, inv_freq: Optional[torch.Tensor], rot: int, head_norm: bool, eps: float,
+                 v_keep: Optional[torch.Tensor], v_first: Optional[torch.Tensor], lam: Optional[torch.Tensor],
+                 slot_mapping: Optional[torch.Tensor], q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                 nh: int, nkv: int, dk: int, dv: int) -> None:
+    """From the float32 q|k|v projection of a step's rows to the attention kernel's inputs: optional bias,
+    optional norm over the whole q and k projections (weights wq, wk), rotation of the first ``rot``
+    dimensions of every head, optional per-head norm without weights, optional mixing of the values with
+    ``v_first`` by ``lam``; q to ``q_out`` [T, nh*HD] and k, v to the rows' page slots, padded with zeros to the
+    cache's head size HD (csrc/cuda/attn_prepare.cu)."""
+    _cuda(proj, bias, wq, wk, positions, inv_freq, v_keep, v_first, lam, slot_mapping, q_out, k_cache, v_cache)
+    T = q_out.shape[0]
+    HD, B = k_cache.shape[3], k_cache.shape[2]
+    n = nh * dk + nkv * dk + nkv * dv
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] >= n and proj.shape[0] >= T, "attn_prepare: proj float32 [T, q|k|v]")
+    for t, m in ((bias, n), (wq, nh * dk), (wk, nkv * dk), (lam, 1)):
+        _need(t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == m), "attn_prepare: float32 vectors")
+    _need((wq is None) == (wk is None) and (v_first is None) == (lam is None), "attn_prepare: arguments that come in pairs")
+    for t in (v_keep, v_first):
+        _need(t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.shape == (T, nkv * dv)), "attn_prepare: values float32 [T, nkv*dv]")
+    _need(q_out.is_contiguous() and q_out.shape == (T, nh * HD) and q_out.dtype == k_cache.dtype == v_cache.dtype
+          and k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.shape[1] == nkv and v_cache.shape == k_cache.shape
+          and HD >= max(dk, dv), "attn_prepare: outputs")
+    _need(positions.dtype == _I32 and positions.numel() >= T and (slot_mapping is None or (slot_mapping.dtype == _I32 and slot_mapping.numel() >= T)),
+          "attn_prepare: positions / slot_mapping int32 [T]")
+    _need(inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == rot), "attn_prepare: inv_freq float32 [rot/2]")
+    fn = getattr(_lib(), "kvcm_attn_prepare_" + _suffix(q_out))
+    _check(fn(_p(proj), proj.stride(0), _p(bias), _p(wq), _p(wk), _p(positions), _p(inv_freq), int(rot), int(bool(head_norm)),
+              ctypes.c_float(eps), _p(v_keep), _p(v_first), _p(lam), _p(slot_mapping), B, _p(q_out), _p(k_cache), _p(v_cache),
+              T, nh, nkv, dk, dv, HD, _stream()), "attn_prepare", f"(nh={nh}, nkv={nkv}, dk={dk}, dv={dv}, HD={HD})")

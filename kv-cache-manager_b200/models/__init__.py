@@ -1,5 +1,5 @@
 """Architectures assembled from parts.  Importing this package registers them."""
 from .spec import ModelSpec, TensorBinding
-from . import llama, tolanex
+from . import bifatar, llama, tolanex
 
-__all__ = ["ModelSpec", "TensorBinding", "llama", "tolanex"]
+__all__ = ["ModelSpec", "TensorBinding", "llama", "tolanex", "bifatar"]

@@ -3,15 +3,16 @@ from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, Blo
                    FeedForward, GroupView, LayerCall, Mixer, Norm, ParamSpec, Part,
                    PositionEncoding, Registry, SiteCache, StateSpec, StepContext)
 from .linear import Linear, matmul_nt
-from .norm import OutputRMSNorm, RMSNorm
+from .norm import DynamicTanh, OutputRMSNorm, RMSNorm
 from .rope import NoPositionEncoding, RotaryEmbedding
-from .attention import PagedAttention
-from .delta import GatedDeltaMixer
+from .attention import GeneralAttention, PagedAttention
+from .delta import ChannelDecayDeltaMixer, GatedDeltaMixer, SideBySideMixer
+from .ssm import Mamba2Mixer
 from .latent_attention import LatentAttention
-from .mlp import GatedMLP
+from .mlp import DenseMLP, GatedMLP
 from .moe import RoutedExperts
 from .embedding import Embedding, LMHead, SummedEmbedding
-from .block import OutputNormBlock, PreNormBlock
+from .block import OutputNormBlock, ParallelBlock, PreNormBlock
 
 __all__ = [
     "BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITION_ENCODINGS", "Block", "CacheSpec",
@@ -19,5 +20,6 @@ __all__ = [
     "PositionEncoding", "Registry", "SiteCache", "StateSpec", "StepContext", "Linear", "matmul_nt",
     "RMSNorm", "NoPositionEncoding", "RotaryEmbedding", "PagedAttention", "GatedMLP", "Embedding",
     "LMHead", "PreNormBlock", "OutputRMSNorm", "OutputNormBlock", "SummedEmbedding", "GatedDeltaMixer",
-    "LatentAttention", "RoutedExperts",
+    "LatentAttention", "RoutedExperts", "DynamicTanh", "GeneralAttention", "ChannelDecayDeltaMixer",
+    "SideBySideMixer", "Mamba2Mixer", "DenseMLP", "ParallelBlock",
 ]

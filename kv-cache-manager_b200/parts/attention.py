@@ -16,7 +16,7 @@ import torch
 
 from ..kernels import library as K
 from .base import CacheSpec, MIXERS, Mixer, PositionEncoding, SiteCache, StepContext
-from .linear import Linear
+from .linear import Linear, matmul_nt
 
 
 @MIXERS.register("attention")
@@ -60,3 +60,106 @@ class PagedAttention(Mixer):
         K.paged_attention(qkv, out, site.k, site.v, g.block_tables, ctx, self.nh, self.nkv, self.hd,
                           self.scale, self.window)
         return self.o.forward(out, ctx)
+
+
+def padded_head_dim(n: int) -> int:
+    """The cache's head size for heads of ``n`` elements: the next size that the tensor-core attention
+    kernels take (multiples of 16 up to 128, of 32 up to 256), else the next multiple of 8."""
+    if n <= 128:
+        return (n + 15) // 16 * 16
+    if n <= 256:
+        return (n + 31) // 32 * 32
+    return (n + 7) // 8 * 8
+
+
+@MIXERS.register("attention_general")
+class GeneralAttention(Mixer):
+    """Grouped-query softmax attention over the paged cache with the options that other designs add,
+    each a constructor parameter:
+
+    * query/key heads of ``dk`` elements and value heads of ``dv`` (the cache's head size is
+      ``padded_head_dim(max(dk, dv))``; the elements beyond a head's own are zero, which changes no
+      score and leaves the output's extra columns zero; the output product's matrix is padded with
+      zero columns once, at load);
+    * ``bias``: q, k and v projections with a bias;
+    * ``proj_norm``: q <- w_q * q / sqrt(mean(q^2) + eps) over the WHOLE q projection (all heads at
+      once), k likewise, before the rotation;
+    * a rotary ``position`` that may cover only the first dimensions of a head;
+    * ``head_norm``: q and k of every head divided by their root mean square (no weights), after the
+      rotation;
+    * ``softcap``: score <- cap * tanh(score / cap) after the scale;
+    * ``window``: row i sees keys j with 0 <= i - j < window;
+    * ``sink``: a learned number per head whose exponential joins the softmax's denominator (no key, no
+      value, not scaled, not capped);
+    * ``value_mix``: "source" leaves this layer's values (as projected) in ``ctx.shared[mix_key]`` for later
+      layers of the same step; "mix" replaces v by (1 - lambda) v + lambda v_source before it is cached.
+
+    Projection, norms, rotation, mixing and the cache write are one kernel between the q|k|v product
+    (float32 result) and the attention kernel; softmax, cap and sink are float32 inside it."""
+
+    def __init__(self, hidden: int, num_heads: int, num_kv_heads: int, dk: int, dv: int,
+                 position: PositionEncoding, scale: Optional[float] = None, window: int = 0, softcap: float = 0.0,
+                 sink: bool = False, bias: bool = False, proj_norm: bool = False, head_norm: bool = False,
+                 norm_eps: float = 1e-6, value_mix: Optional[str] = None, mix_key: str = "v_first") -> None:
+        super().__init__()
+        if num_kv_heads < 1 or num_heads % num_kv_heads:
+            raise ValueError(f"attention: {num_heads} query heads are not a multiple of {num_kv_heads} KV heads")
+        if value_mix not in (None, "source", "mix"):
+            raise ValueError(f"attention: unknown value_mix {value_mix!r}")
+        if getattr(position, "interleaved", False) or getattr(position, "rotary_dim", 0) > dk:
+            raise ValueError("attention_general: rotate-half pairs within the head's own size only")
+        self.hidden, self.nh, self.nkv, self.dk, self.dv = hidden, num_heads, num_kv_heads, dk, dv
+        self.hd = padded_head_dim(max(dk, dv))
+        self.window, self.softcap = int(window or 0), float(softcap or 0.0)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(dk)
+        self.has_sink, self.has_bias, self.proj_norm, self.head_norm = bool(sink), bool(bias), bool(proj_norm), bool(head_norm)
+        self.norm_eps, self.value_mix, self.mix_key = float(norm_eps), value_mix, mix_key
+        self.position = self.add_child("position", position)
+        nq, nk, nv = num_heads * dk, num_kv_heads * dk, num_kv_heads * dv
+        self.qkv = self.add_child("qkv", Linear(hidden, nq + nk + nv, hidden ** -0.5))
+        self.o = self.add_child("o", Linear(num_heads * dv, hidden, (num_heads * dv) ** -0.5))
+        if self.has_bias:
+            self.declare("bias", (nq + nk + nv,), ("normal", 0.1), "vector")
+        if self.proj_norm:
+            self.declare("q_norm", (nq,), ("ones_jitter", 0.1), "vector")
+            self.declare("k_norm", (nk,), ("ones_jitter", 0.1), "vector")
+        if self.has_sink:
+            self.declare("sink", (num_heads,), ("normal", 1.0), "vector")
+        if value_mix is not None:
+            self.declare("vmix", (), ("normal", 0.3), "vector")       # read by "mix" layers only
+        self._f32 = {}
+        self._o_weight = None
+
+    def cache_spec(self) -> CacheSpec:
+        return CacheSpec(self.nkv, self.hd, self.window)
+
+    def prepare(self, device, dtype) -> None:
+        super().prepare(device, dtype)
+        self._f32 = {n: self.param(n).to(device=device, dtype=torch.float32).reshape(-1).contiguous()
+                     for n in self.param_specs()}
+        w = self.o.param("weight")
+        if self.hd != self.dv:                              # zero columns where the attention output is padding
+            wide = torch.zeros((self.hidden, self.nh, self.hd), dtype=w.dtype, device=w.device)
+            wide[:, :, :self.dv] = w.view(self.hidden, self.nh, self.dv)
+            w = wide.view(self.hidden, self.nh * self.hd)
+        self._o_weight = w
+
+    def forward(self, h: torch.Tensor, ctx: StepContext, site: SiteCache) -> torch.Tensor:
+        g = ctx.groups[site.group]
+        pos, f = self.position, self._f32
+        T = h.shape[0]
+        proj = self.qkv.forward(h, ctx, out_dtype=torch.float32)
+        keep = first = None
+        if self.value_mix == "source":
+            keep = ctx.shared[self.mix_key] = torch.empty((T, self.nkv * self.dv), dtype=torch.float32, device=h.device)
+        elif self.value_mix == "mix":
+            first = ctx.shared[self.mix_key]
+        q = torch.empty((T, self.nh * self.hd), dtype=h.dtype, device=h.device)
+        K.attn_prepare(proj, f.get("bias"), f.get("q_norm"), f.get("k_norm"), ctx.positions, pos.inv_freq,
+                       pos.rotary_dim if pos.inv_freq is not None else 0, self.head_norm, self.norm_eps, keep, first,
+                       f["vmix"] if first is not None else None, g.slot_mapping if site.writes else None, q, site.k, site.v,
+                       self.nh, self.nkv, self.dk, self.dv)
+        out = torch.empty((T, self.nh * self.hd), dtype=h.dtype, device=h.device)
+        K.paged_attention(q, out, site.k, site.v, g.block_tables, ctx, self.nh, self.nkv, self.hd, self.scale,
+                          self.window, self.softcap, f.get("sink"))
+        return matmul_nt(out, self._o_weight, torch.float32, ctx.options)

@@ -180,6 +180,8 @@ class StepContext:
     prev_tokens: Optional[torch.Tensor] = None   # per row: the request's token one position earlier (-1 at position 0)
     h_stream: Optional[torch.Tensor] = None      # storage-dtype copy of the residual stream, kept current by blocks
                                                  # whose sublayers read the stream itself (None: nobody keeps one)
+    shared: Dict[str, Any] = field(default_factory=dict)   # what a layer leaves for later layers of the SAME step
+                                                           # (per-row tensors, e.g. an early layer's values)
 
 
 # ------------------------------------------------------------------------------ registries

@@ -64,3 +64,26 @@ class OutputNormBlock(Block):
         if self.ffn is not None:
             self.norm2.forward(x, self.ffn.forward(x if h is None else h, ctx), keep)
         return None
+
+
+@BLOCKS.register("parallel")
+class ParallelBlock(Block):
+    """x += mixer(h) + ffn(h) with ONE norm, h = norm1(x): both sublayers read the same normalised rows.
+    Their float32 outputs are not summed here: they are handed on as a list of (tensor, scale) pairs and
+    added into the stream inside the next norm kernel (a mixer made of several branches returns such a
+    list itself).  ``norm1`` must take such a list (the "dyt" norm does).  ``ffn`` may be None."""
+
+    def __init__(self, norm1: Norm, mixer: Mixer, ffn: Optional[FeedForward] = None) -> None:
+        super().__init__()
+        self.norm1 = self.add_child("norm1", norm1)
+        self.mixer = self.add_child("mixer", mixer)
+        self.ffn = self.add_child("ffn", ffn) if ffn is not None else None
+
+    def forward(self, x: torch.Tensor, pending, ctx: StepContext, site: SiteCache):
+        h = torch.empty(x.shape, dtype=ctx.dtype, device=x.device)
+        self.norm1.forward(x, pending, h)
+        y = self.mixer.forward(h, ctx, site)
+        out = list(y) if isinstance(y, (list, tuple)) else [(y, 1.0)]
+        if self.ffn is not None:
+            out.append((self.ffn.forward(h, ctx, out_dtype=torch.float32), 1.0))
+        return out

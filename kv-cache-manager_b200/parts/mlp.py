@@ -49,3 +49,21 @@ class GatedMLP(FeedForward):
         else:
             K.silu_mul(self.gate_up.forward(h, ctx), act)
         return self.down.forward(act, ctx, out_dtype)
+
+
+@FEED_FORWARDS.register("dense_mlp")
+class DenseMLP(FeedForward):
+    """Ungated feed-forward: down( act(x Wu^T) ); act "relu2" = max(z, 0)^2."""
+
+    def __init__(self, hidden: int, intermediate: int, activation: str = "relu2") -> None:
+        super().__init__()
+        if activation != "relu2":
+            raise ValueError(f"dense_mlp: activation '{activation}' has no kernel (only 'relu2')")
+        self.hidden, self.intermediate = hidden, intermediate
+        self.up = self.add_child("up", Linear(hidden, intermediate, hidden ** -0.5))
+        self.down = self.add_child("down", Linear(intermediate, hidden, intermediate ** -0.5))
+
+    def forward(self, h: torch.Tensor, ctx: StepContext, out_dtype=None) -> torch.Tensor:
+        z = self.up.forward(h, ctx)
+        K.relu_sq(z, z)
+        return self.down.forward(z, ctx, out_dtype)

@@ -43,3 +43,32 @@ class OutputRMSNorm(Norm):
         if rows is not None or pending is None:
             raise ValueError("rmsnorm_output: needs the sublayer's output for every row")
         K.rms_scale_add(x, pending, self.param("weight"), out, self.eps, self.mult)
+
+
+@NORMS.register("dyt")
+class DynamicTanh(Norm):
+    """A norm without statistics: out = tanh(alpha * x) * w + b, with one learned number alpha and
+    vectors w, b.  ``pending`` is what the layer before left to be added to the stream first: None,
+    one float32 tensor, or a list of (float32 tensor, scale) pairs (a block whose sublayers' outputs
+    are summed hands them on unsummed); the sum, the stream and the tanh are float32."""
+
+    def __init__(self, hidden: int, init=("ones",)) -> None:
+        super().__init__()
+        self.hidden = hidden
+        self.declare("weight", (hidden,), init, "vector")
+        self.declare("bias", (hidden,), ("normal", 0.02), "vector")
+        self.declare("alpha", (), ("ones_jitter", 0.1), "vector")
+        self._f32 = {}
+
+    def prepare(self, device, dtype) -> None:
+        super().prepare(device, dtype)
+        self._f32 = {n: self.param(n).to(device=device, dtype=torch.float32).reshape(-1).contiguous()
+                     for n in ("weight", "bias", "alpha")}
+
+    def forward(self, x: torch.Tensor, pending, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+        if pending is None:
+            pending = []
+        elif isinstance(pending, torch.Tensor):
+            pending = [(pending if pending.dtype == torch.float32 else pending.float(), 1.0)]
+        f = self._f32
+        K.dyt_norm(x, pending, f["weight"], f["bias"], f["alpha"], out, rows)
