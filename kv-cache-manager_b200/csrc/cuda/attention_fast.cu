@@ -32,7 +32,9 @@ struct DecodeParams {
   const int* seq_ctx_len;
   float* part_o; float* part_ml;
   int nh, nkv, block_size, window, part_size, num_parts;
-  float scale_log2;
+  float scale_log2;                    // what a score is multiplied by on its way into exp2
+  float cap_pre;                       // > 0: capped scores, s <- tanh(s * cap_pre) first (cap_pre = scale / cap, scale_log2 = cap * log2 e)
+  const float* sink;                   // per head, or null: exp(sink) joins the denominator where the result is normalised
   int log2_block;                      // log2(block_size) when it is a power of two, else -1
   int cluster_merge;                   // the partitions of a (request, head group) are one cluster
 };
@@ -96,6 +98,7 @@ __device__ __forceinline__ void cluster_merge_tail(const DecodeParams& p, int se
       acc.z = __fmaf_rn(f, op[i].z, acc.z); acc.w = __fmaf_rn(f, op[i].w, acc.w);
       L = __fmaf_rn(f, lp[i], L);
     }
+    if (p.sink && M != -INFINITY) L += fast_exp2(p.sink[head0 + r] * 1.4426950408889634f - M);
     const float inv = L > 0.f ? 1.f / L : 0.f;
     store_out4(p.out + size_t(seq) * p.out_stride + size_t(head0 + r) * HD + d, acc.x * inv, acc.y * inv, acc.z * inv,
                acc.w * inv);
@@ -251,14 +254,15 @@ attn_decode_kernel(DecodeParams p) {
 #pragma unroll
         for (int h = 0; h < 2; ++h)
 #pragma unroll
-          for (int j = 0; j < 4; ++j) s[h][j] *= p.scale_log2;
+          for (int j = 0; j < 4; ++j) s[h][j] = (p.cap_pre > 0.f ? fast_tanh(s[h][j] * p.cap_pre) : s[h][j]) * p.scale_log2;
       } else {
 #pragma unroll
         for (int h = 0; h < 2; ++h)
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const int key = kb + 8 * h + 2 * t4 + (j & 1);
-            s[h][j] = (key >= begin && key < end) ? s[h][j] * p.scale_log2 : -INFINITY;
+            const float capped = (p.cap_pre > 0.f ? fast_tanh(s[h][j] * p.cap_pre) : s[h][j]) * p.scale_log2;
+            s[h][j] = (key >= begin && key < end) ? capped : -INFINITY;
           }
       }
       uint32_t pa[4];
@@ -318,6 +322,7 @@ attn_decode_kernel(DecodeParams p) {
         bl[r] = L;
       }
     } else if (p.num_parts == 1) {
+      if (p.sink && M != -INFINITY) L += fast_exp2(p.sink[head] * 1.4426950408889634f - M);
       const float inv = L > 0.f ? 1.f / L : 0.f;
       store_out4(p.out + size_t(seq) * p.out_stride + size_t(head) * HD + d, acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
     } else {
@@ -334,7 +339,8 @@ attn_decode_kernel(DecodeParams p) {
 
 // Merges the partitions of one (request, head): out = sum_p 2^(m_p - M) o_p / sum_p 2^(m_p - M) l_p.
 __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                         bf16* __restrict__ out, int out_stride, int nh, int hd, int num_parts) {
+                                         bf16* __restrict__ out, int out_stride, int nh, int hd, int num_parts,
+                                         const float* __restrict__ sink) {
   pdl_launch_dependents();
   pdl_wait();
   const int seq = blockIdx.x, head = blockIdx.y;
@@ -350,6 +356,7 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const
       acc = __fmaf_rn(f, part_o[(base + i) * hd + d], acc);
       L = __fmaf_rn(f, part_ml[(base + i) * 2 + 1], L);
     }
+    if (sink && M != -INFINITY) L += exp2f(sink[head] * 1.4426950408889634f - M);
     out[size_t(seq) * out_stride + size_t(head) * hd + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
   }
 }
@@ -442,11 +449,14 @@ KVCM_API int kvcm_attention_decode_cluster_parts(void) { return kMaxClusterParts
 
 // `scratch`: kvcm_attention_decode_scratch_floats() floats, needed when num_parts > 1 unless the
 // merge runs inside a cluster (cluster_merge != 0 and num_parts <= kvcm_attention_decode_cluster_parts()).
-KVCM_API int kvcm_attention_decode_bf16(const void* q, int q_stride, void* out, int out_stride,
-                                        const void* k_cache, const void* v_cache, const int* block_tables,
-                                        int max_blocks, const int* seq_ctx_len, int seqs, int nh, int nkv,
-                                        int hd, int block_size, float scale, int window, int part_size,
-                                        int num_parts, float* scratch, int cluster_merge, void* stream) {
+// `softcap` > 0: scaled scores are capped as cap * tanh(score / cap); `sink` (per head, optional): exp(sink)
+// joins the softmax's denominator.
+KVCM_API int kvcm_attention_decode_capped_bf16(const void* q, int q_stride, void* out, int out_stride,
+                                               const void* k_cache, const void* v_cache, const int* block_tables,
+                                               int max_blocks, const int* seq_ctx_len, int seqs, int nh, int nkv,
+                                               int hd, int block_size, float scale, int window, int part_size,
+                                               int num_parts, float* scratch, int cluster_merge, float softcap,
+                                               const float* sink, void* stream) {
   if (seqs == 0) return 0;
   static int sm_count = 0;
   if (sm_count == 0) {
@@ -465,7 +475,9 @@ KVCM_API int kvcm_attention_decode_bf16(const void* q, int q_stride, void* out, 
   p.part_o = scratch; p.part_ml = scratch ? scratch + (size_t)seqs * nh * num_parts * hd : nullptr;
   p.nh = nh; p.nkv = nkv; p.block_size = block_size; p.window = window;
   p.part_size = part_size; p.num_parts = num_parts; p.cluster_merge = cluster_merge;
-  p.scale_log2 = scale * 1.4426950408889634f;
+  p.scale_log2 = (softcap > 0.f ? softcap : scale) * 1.4426950408889634f;
+  p.cap_pre = softcap > 0.f ? scale / softcap : 0.f;
+  p.sink = sink;
   p.log2_block = -1;
   for (int b = 0; b < 16; ++b) if ((1 << b) == block_size) p.log2_block = b;
   int rc = KVCM_ERR_UNSUPPORTED;
@@ -474,6 +486,15 @@ KVCM_API int kvcm_attention_decode_bf16(const void* q, int q_stride, void* out, 
 #undef X
   if (rc != 0 || num_parts == 1 || cluster_merge) return rc;
   return pdl_launch(attn_decode_merge_kernel, dim3(seqs, nh), dim3(hd < 64 ? 32 : 64), 0, (cudaStream_t)stream,
-                    (const float*)p.part_o, (const float*)p.part_ml, p.out, out_stride, nh, hd, num_parts);
+                    (const float*)p.part_o, (const float*)p.part_ml, p.out, out_stride, nh, hd, num_parts, p.sink);
 }
 
+KVCM_API int kvcm_attention_decode_bf16(const void* q, int q_stride, void* out, int out_stride,
+                                        const void* k_cache, const void* v_cache, const int* block_tables,
+                                        int max_blocks, const int* seq_ctx_len, int seqs, int nh, int nkv,
+                                        int hd, int block_size, float scale, int window, int part_size,
+                                        int num_parts, float* scratch, int cluster_merge, void* stream) {
+  return kvcm_attention_decode_capped_bf16(q, q_stride, out, out_stride, k_cache, v_cache, block_tables, max_blocks, seq_ctx_len,
+                                           seqs, nh, nkv, hd, block_size, scale, window, part_size, num_parts, scratch,
+                                           cluster_merge, 0.f, nullptr, stream);
+}

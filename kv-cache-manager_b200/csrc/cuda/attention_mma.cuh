@@ -154,6 +154,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// tanh from one exponential and one reciprocal (absolute error of a few 1e-7: all that a capped score needs).
+__device__ __forceinline__ float fast_tanh(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(r) : "f"(fast_exp2(x * 2.8853900817779268f) + 1.f));
+  return fmaf(-2.f, r, 1.f);
+}
+
 // One warp: S(16 x 16 keys) = Q(16 x HD) * K(16 keys x HD)^T.  `qa` holds the A fragments of Q
 // for every 16-wide slice of HD; `ktile` points at the first of the 16 keys in the shared tile.
 // s[0] = keys 0..7, s[1] = keys 8..15 (accumulator layout).

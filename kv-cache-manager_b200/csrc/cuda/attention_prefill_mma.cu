@@ -20,7 +20,9 @@ struct PrefillParams {
   const int* tile_seq; const int* tile_q0;
   const int* seq_q_start; const int* seq_q_len; const int* seq_ctx_len;
   int nh, nkv, block_size, window;
-  float scale_log2;
+  float scale_log2;                 // what a score is multiplied by on its way into exp2
+  float cap_pre;                    // > 0: capped scores, s <- tanh(s * cap_pre) first (cap_pre = scale / cap, scale_log2 = cap * log2 e)
+  const float* sink;                // per head, or null: exp(sink) joins every row's denominator at the end
   int log2_block;
 };
 
@@ -122,7 +124,7 @@ attn_prefill_kernel(PrefillParams p) {
       for (int n = 0; n < kKeyTile / 8; ++n)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          float v = s[n][j] * p.scale_log2;
+          float v = (p.cap_pre > 0.f ? fast_tanh(s[n][j] * p.cap_pre) : s[n][j]) * p.scale_log2;
           if (needs_mask) {
             const int key = t0 + 8 * n + 2 * t4 + (j & 1);
             const int rp = row_pos[j >> 1];
@@ -178,6 +180,7 @@ attn_prefill_kernel(PrefillParams p) {
   for (int r = 0; r < 2; ++r) {
     const int local = warp * 16 + g + 8 * r;
     if (local >= rows_here) continue;
+    if (p.sink && m[r] != -INFINITY) l[r] += fast_exp2(p.sink[head] * 1.4426950408889634f - m[r]);
     const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
     bf16* dst = p.out + size_t(q_start + q0 + local) * p.out_stride + size_t(head) * HD + 2 * t4;
 #pragma unroll
@@ -212,7 +215,7 @@ KVCM_API int kvcm_attention_prefill_bf16(const void* q, int q_stride, void* out,
                                          int max_blocks, const int* tile_seq, const int* tile_q0,
                                          const int* seq_q_start, const int* seq_q_len, const int* seq_ctx_len,
                                          int tiles, int nh, int nkv, int hd, int block_size, float scale,
-                                         int window, void* stream) {
+                                         int window, float softcap, const float* sink, void* stream) {
   if (tiles == 0) return 0;
   if (nkv <= 0 || nh % nkv) return KVCM_ERR_UNSUPPORTED;
   PrefillParams p;
@@ -221,7 +224,9 @@ KVCM_API int kvcm_attention_prefill_bf16(const void* q, int q_stride, void* out,
   p.block_tables = block_tables; p.max_blocks = max_blocks; p.tile_seq = tile_seq; p.tile_q0 = tile_q0;
   p.seq_q_start = seq_q_start; p.seq_q_len = seq_q_len; p.seq_ctx_len = seq_ctx_len;
   p.nh = nh; p.nkv = nkv; p.block_size = block_size; p.window = window;
-  p.scale_log2 = scale * 1.4426950408889634f;
+  p.scale_log2 = (softcap > 0.f ? softcap : scale) * 1.4426950408889634f;
+  p.cap_pre = softcap > 0.f ? scale / softcap : 0.f;
+  p.sink = sink;
   p.log2_block = -1;
   for (int b = 0; b < 16; ++b) if ((1 << b) == block_size) p.log2_block = b;
   int rc = KVCM_ERR_UNSUPPORTED;

@@ -52,13 +52,23 @@ struct PrefillTcParams {
   const int* tile_seq; const int* tile_q0;                 // tiles of 64 rows; a block takes an even one and its successor
   const int* seq_q_start; const int* seq_q_len; const int* seq_ctx_len;
   int nh, nkv, block_size, window;
-  float scale_log2;
+  float scale_log2;                 // what a score is multiplied by on its way into exp2
+  float cap_pre;                    // > 0: scores are capped, s <- tanh(s * cap_pre) first (cap_pre = scale / cap and
+                                    // scale_log2 = cap * log2(e))
+  const float* sink;                // per head, or null: exp(sink) joins the row's denominator at the end
 };
 
 __device__ __forceinline__ float fa_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
+}
+
+// tanh from one exponential and one reciprocal (absolute error of a few 1e-7, all that a capped score needs)
+__device__ __forceinline__ float fa_tanh(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(r) : "f"(fa_exp2(x * 2.8853900817779268f) + 1.f));
+  return fmaf(-2.f, r, 1.f);
 }
 
 // Two blocks of six warps share an SM at head_dim 64.  Registers are handed out per scheduler, a
@@ -239,6 +249,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
       __syncwarp();
       if (lane == 0) tc5::mbar_arrive(&s_free[n & 1]);                // S_(n+2) may be written
+      if (p.cap_pre > 0.f) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[c][i] = __float_as_uint(fa_tanh(__uint_as_float(v[c][i]) * p.cap_pre));
+      }
       const int key0 = (j0 + n) * kFaKeys;
       // the keys of this tile that the row may see: [a, b) relative to the tile
       const int a = max(first, lo) - key0, b = min(pos + 1, hi) - key0;
@@ -350,6 +366,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (!all_o && !abort_flag && lane == 0) fail(6);
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     if (all_o) {
+      if (p.sink && m != -INFINITY) l += fa_exp2(p.sink[head] * 1.4426950408889634f - m);
       const float inv = l > 0.f ? 1.f / l : 0.f;
       bf16* dst = p.out + size_t(q_start + q0 + r) * p.out_stride + size_t(head) * HD;
 #pragma unroll 1
@@ -406,7 +423,8 @@ KVCM_API int kvcm_attention_prefill_tcgen05_bf16(const void* q, int q_stride, in
                                                  const int* block_tables, int max_blocks, const int* tile_seq,
                                                  const int* tile_q0, const int* seq_q_start, const int* seq_q_len,
                                                  const int* seq_ctx_len, int tiles, int nh, int nkv, int hd,
-                                                 int block_size, float scale, int window, void* stream) {
+                                                 int block_size, float scale, int window, float softcap, const float* sink,
+                                                 void* stream) {
   if (tiles == 0) return 0;
   if (!kvcm_attention_tcgen05_supports(hd, block_size) || nkv <= 0 || nh % nkv) return KVCM_ERR_UNSUPPORTED;
   if ((q_stride % 8) || (out_stride % 8) || (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) ||
@@ -426,7 +444,9 @@ KVCM_API int kvcm_attention_prefill_tcgen05_bf16(const void* q, int q_stride, in
   p.block_tables = block_tables; p.max_blocks = max_blocks; p.tile_seq = tile_seq; p.tile_q0 = tile_q0;
   p.seq_q_start = seq_q_start; p.seq_q_len = seq_q_len; p.seq_ctx_len = seq_ctx_len;
   p.nh = nh; p.nkv = nkv; p.block_size = block_size; p.window = window;
-  p.scale_log2 = scale * 1.4426950408889634f;
+  p.scale_log2 = (softcap > 0.f ? softcap : scale) * 1.4426950408889634f;
+  p.cap_pre = softcap > 0.f ? scale / softcap : 0.f;
+  p.sink = sink;
   const int KB = hd / 64;
   // 112 KB at head_dim 64 (two blocks fit an SM exactly), 192 KB at 128
   const size_t smem = size_t(KB + 2) * kFaTileBytes + size_t(2) * kFaStages * KB * kFaKvBlock;

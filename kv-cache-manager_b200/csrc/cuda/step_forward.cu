@@ -47,9 +47,10 @@ int kvcm_attention_decode_bf16(const void*, int, void*, int, const void*, const 
 int kvcm_attention_tcgen05_supports(int, int);
 int kvcm_attention_prefill_tcgen05_bf16(const void*, int, int, void*, int, const void*, const void*, int, const int*, int,
                                         const int*, const int*, const int*, const int*, const int*, int, int, int, int, int,
-                                        float, int, void*);
+                                        float, int, float, const float*, void*);
 int kvcm_attention_prefill_bf16(const void*, int, void*, int, const void*, const void*, const int*, int, const int*,
-                                const int*, const int*, const int*, const int*, int, int, int, int, int, float, int, void*);
+                                const int*, const int*, const int*, const int*, int, int, int, int, int, float, int, float, const float*,
+                                void*);
 int kvcm_gemm_stream_supports(int, int, int);
 int kvcm_gemm_stream_fused_supports(int, int, int);
 int kvcm_gemm_stream_bf16(const void*, const void*, void*, int, int, int, int, int, int, int, int, void*);
@@ -184,10 +185,10 @@ int attention(const KvcmForwardArgs& a, const KvcmForwardLayer& L, const void* q
       return kvcm_attention_prefill_tcgen05_bf16(q, q_stride, a.rows, a.attn, a.nh * a.hd, L.k_cache, L.v_cache, L.num_pages,
                                                  tables, a.max_blocks, a.tile_seq, a.tile_q0, a.seq_q_start, a.seq_q_len,
                                                  a.seq_ctx_len, a.prefill_tiles, a.nh, a.nkv, a.hd, a.block_size, a.scale,
-                                                 L.window, s);
+                                                 L.window, 0.f, nullptr, s);
     return kvcm_attention_prefill_bf16(q, q_stride, a.attn, a.nh * a.hd, L.k_cache, L.v_cache, tables, a.max_blocks,
                                        a.tile_seq, a.tile_q0, a.seq_q_start, a.seq_q_len, a.seq_ctx_len, a.prefill_tiles,
-                                       a.nh, a.nkv, a.hd, a.block_size, a.scale, L.window, s);
+                                       a.nh, a.nkv, a.hd, a.block_size, a.scale, L.window, 0.f, nullptr, s);
   }
   return rc;
 }

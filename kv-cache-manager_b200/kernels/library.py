@@ -395,16 +395,15 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
     rest are the rows of longer portions.  ``ctx.options['attention']``: 'plain' forces the plain
     kernel for every row; float32 storage always uses it (the true 32-bit path)."""
     mode = ctx.options.get("attention", "auto")
-    if mode == "plain" or q.dtype == torch.float32 or not fast_attention_supported(nh, nkv, hd, k_cache.shape[2]) \
-            or softcap > 0.0 or sink is not None:
+    if mode == "plain" or q.dtype == torch.float32 or not fast_attention_supported(nh, nkv, hd, k_cache.shape[2]):
         attention_plain(q, out, k_cache, v_cache, block_tables, ctx.row_seq, ctx.positions,
                         nh, nkv, hd, scale, window, softcap, sink)
         return
     nd = ctx.decode_seqs
     if nd > 0:
-        attention_decode(q[:nd], out[:nd], k_cache, v_cache, block_tables, ctx, nh, nkv, hd, scale, window)
+        attention_decode(q[:nd], out[:nd], k_cache, v_cache, block_tables, ctx, nh, nkv, hd, scale, window, softcap, sink)
     if ctx.rows > nd:
-        attention_prefill(q, out, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, scale, window)
+        attention_prefill(q, out, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, scale, window, softcap, sink)
 
 
 def fast_attention_supported(nh: int, nkv: int, hd: int, block_size: int) -> bool:
@@ -466,9 +465,12 @@ def decode_partitions(seqs: int, nh: int, nkv: int, hd: int, max_ctx: int, devic
 
 def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                      block_tables: torch.Tensor, ctx, nh: int, nkv: int, hd: int, scale: float,
-                     window: int = 0) -> None:
-    """Single-row entries: q/out hold one row per request, in the order of the batch's entries."""
-    _cuda(q, out, k_cache, v_cache, block_tables)
+                     window: int = 0, softcap: float = 0.0, sink: Optional[torch.Tensor] = None) -> None:
+    """Single-row entries: q/out hold one row per request, in the order of the batch's entries.
+    ``softcap`` / ``sink`` as in ``attention_plain``."""
+    _cuda(q, out, k_cache, v_cache, block_tables, sink)
+    _need(sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == nh),
+          "attention_decode: sink float32 [heads]")
     S = q.shape[0]
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16,
           "attention_decode: bfloat16 only")
@@ -484,10 +486,11 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
     if parts > 1 and not in_cluster:
         n = S * nh * parts * (hd + 2)          # partial outputs + (max, sum) per partition
         scratch = torch.empty(n, dtype=torch.float32, device=q.device)
-    rc = _lib().kvcm_attention_decode_bf16(
+    rc = _lib().kvcm_attention_decode_capped_bf16(
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_cache), _p(v_cache), _p(block_tables),
         block_tables.shape[1], _p(ctx.seq_ctx_len), S, nh, nkv, hd, k_cache.shape[2],
-        ctypes.c_float(scale), int(window), size, parts, _p(scratch), int(in_cluster), _stream())
+        ctypes.c_float(scale), int(window), size, parts, _p(scratch), int(in_cluster), ctypes.c_float(softcap), _p(sink),
+        _stream())
     _check(rc, "attention_decode", f"(hd={hd}, nh={nh}, nkv={nkv})")
     if parts > 1 and not in_cluster:
         global _launches
@@ -496,11 +499,13 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
 
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                       block_tables: torch.Tensor, ctx, nh: int, nkv: int, hd: int, scale: float,
-                      window: int = 0) -> None:
+                      window: int = 0, softcap: float = 0.0, sink: Optional[torch.Tensor] = None) -> None:
     """Rows of portions longer than one token; q/out are the step's full row arrays.
     ``ctx.options['attn_prefill']``: 'tcgen05' | 'mma' force a kernel; 'auto' takes the tcgen05
     kernel where it supports the sizes (head_dim 64 or 128; pages of 8 to 64 keys dividing 64, or multiples of 64)."""
-    _cuda(q, out, k_cache, v_cache, block_tables)
+    _cuda(q, out, k_cache, v_cache, block_tables, sink)
+    _need(sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == nh),
+          "attention_prefill: sink float32 [heads]")
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16,
           "attention_prefill: bfloat16 only")
     _need(q.stride(1) == 1 and out.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous(),
@@ -515,14 +520,14 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
             _p(q), q.stride(0), q.shape[0], _p(out), out.stride(0), _p(k_cache), _p(v_cache), k_cache.shape[0],
             _p(block_tables), block_tables.shape[1], _p(ctx.tile_seq), _p(ctx.tile_q0), _p(ctx.seq_q_start),
             _p(ctx.seq_q_len), _p(ctx.seq_ctx_len), ctx.prefill_tiles, nh, nkv, hd, B, ctypes.c_float(scale),
-            int(window), _stream())
+            int(window), ctypes.c_float(softcap), _p(sink), _stream())
         _check(rc, "attention_prefill_tcgen05", f"(hd={hd}, nh={nh}, nkv={nkv}, block={B})")
         return
     rc = _lib().kvcm_attention_prefill_bf16(
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_cache), _p(v_cache), _p(block_tables),
         block_tables.shape[1], _p(ctx.tile_seq), _p(ctx.tile_q0), _p(ctx.seq_q_start), _p(ctx.seq_q_len),
         _p(ctx.seq_ctx_len), ctx.prefill_tiles, nh, nkv, hd, B, ctypes.c_float(scale),
-        int(window), _stream())
+        int(window), ctypes.c_float(softcap), _p(sink), _stream())
     _check(rc, "attention_prefill", f"(hd={hd}, nh={nh}, nkv={nkv})")
 
 
