@@ -327,20 +327,87 @@ def llama_work(z, T, ctx, decode):
     }
 
 
+
+# --compare bifatar: the Bifatar design (windowed attention with sink, cap and value mixing; the state-space
+# mixer; attention beside the channel-decay delta rule; tanh norms, one per layer; squared-ReLU feed-forward)
+# beside the Llama decoder at equal width, depth, head count and feed-forward parameter count.
+BIFATAR_SIZES = {
+    "b2048": dict(width=2048, order=("attention", "mamba2", "parallel", "attention"), heads=16, kv_heads=4, dim=128, window=1024,
+                  ssm_heads=64, ssm_vdim=64, ssm_state=128, ssm_groups=8, delta_heads=16, llama_ff=4096),
+    "b4096": dict(width=4096, order=("attention", "mamba2", "parallel"), heads=32, kv_heads=8, dim=128, window=1024,
+                  ssm_heads=128, ssm_vdim=64, ssm_state=128, ssm_groups=8, delta_heads=32, llama_ff=8192),
+}
+
+
+def bifatar_configs(z):
+    """(Bifatar config, Llama config) of one size.  The ungated feed-forward has two matrices where the gated
+    one has three: its inner size is 1.5 times Llama's, so that both read and multiply the same weights."""
+    from kvcm.config import LlamaConfig, config_from_dict
+    D, H, G, d = z["width"], z["heads"], z["kv_heads"], z["dim"]
+    mlp = {"kind": "dense", "ff": z["llama_ff"] * 3 // 2}
+    rot = {"base": 10000.0, "dims": d}
+    layers = []
+    for kind in z["order"]:
+        if kind == "attention":
+            m = {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5 / 4, "rot": rot, "mask": {"size": z["window"]},
+                 "softcap": 30.0, "v_mix": True}
+        elif kind == "mamba2":
+            m = {"heads": z["ssm_heads"], "vdim": z["ssm_vdim"], "state": z["ssm_state"], "groups": z["ssm_groups"], "conv": 4,
+                 "norm_groups": z["ssm_groups"]}
+        else:
+            m = {"left": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5, "rot": rot},
+                 "right": {"heads": z["delta_heads"], "kv_heads": z["delta_heads"], "dim": d, "vdim": d, "conv": 4,
+                           "decay_rank": 64, "gate_rank": 64},
+                 "left_scale": 1.0, "right_scale": 1.0}
+        layers.append({"type": kind, "mixer": m, "mlp": mlp})
+    bif = config_from_dict({"architecture": "Bifatar", "vocab": COMPARE_VOCAB, "width": D, "norm": {"eps": 1e-6}, "layers": layers})
+    lla = LlamaConfig(architecture="LlamaForCausalLM", vocab_size=COMPARE_VOCAB, hidden_size=D, intermediate_size=z["llama_ff"],
+                      num_hidden_layers=len(layers), num_attention_heads=H, num_key_value_heads=G, head_dim=d,
+                      max_position_embeddings=4096, rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=False)
+    return bif, lla
+
+
+def bifatar_work(z, T, ctx, decode):
+    """What the families of one Bifatar step have to do at least: flops, or bytes they must move."""
+    D, H, G, d, W = z["width"], z["heads"], z["kv_heads"], z["dim"], z["window"]
+    n_win = sum(k == "attention" for k in z["order"])
+    n_par = sum(k == "parallel" for k in z["order"])
+    n_ssm = sum(k == "mamba2" for k in z["order"])
+    L = len(z["order"])
+    seen_win = T * min(ctx, W) if decode else sum(min(i + 1, W) for i in range(T))
+    seen_all = T * ctx if decode else T * (T + 1) / 2
+    ssm_state = z["ssm_heads"] * z["ssm_state"] * z["ssm_vdim"]
+    delta_state = z["delta_heads"] * d * d
+    ff = z["llama_ff"] * 3 // 2
+    return {
+        "attention": dict(flops=4.0 * d * H * (seen_win * n_win + seen_all * n_par),
+                          bytes=2.0 * 2 * G * d * (T * min(ctx, W) * n_win + T * ctx * n_par) if decode else None),
+        "state_scan": dict(flops=T * (4.0 * ssm_state * n_ssm + 7.0 * delta_state * n_par),
+                           bytes=8.0 * T * (ssm_state * n_ssm + delta_state * n_par) if decode else None),
+        "feed_forward": dict(flops=2.0 * T * 2 * ff * D * L, bytes=2.0 * 2 * ff * D * L if decode else None),
+        "dyt_norm": dict(flops=None, bytes=T * D * (4.0 * 2 + 4.0 * 2.3 + 2.0) * L),
+    }
+
+
 def compare_main(args) -> int:
     import torch
     from kvcm.config import EngineConfig, KVManagerConfig, SchedulerConfig
     from kvcm.engine import model_from_tensors
     from kvcm.weights import random_tensors
     pk = peaks()
-    out = {"compare": "tolanex beside llama at equal width, depth and active feed-forward size", "dtype": "bf16",
+    first = args.compare
+    sizes, configs, first_work = ((BIFATAR_SIZES, bifatar_configs, bifatar_work) if first == "bifatar"
+                                  else (COMPARE_SIZES, compare_configs, tolanex_work))
+    out = {"compare": f"{first} beside llama at equal width, depth and (active) feed-forward size", "dtype": "bf16",
            "data": "synthetic: random weights, uniform random token ids", "peaks": pk, "sizes": {}}
     steps, warmup = min(args.steps, 200), max(args.warmup, 3)
-    for name, z in COMPARE_SIZES.items():
+    for name, z in sizes.items():
         if args.size not in ("all", name):
             continue
+        if first == "bifatar":
+            z = dict(z, layers=len(z["order"]), top=1, ff=z["llama_ff"], shared=0)      # the keys llama_work reads
         res = {}
-        for arch, cfg in zip(("tolanex", "llama"), compare_configs(z)):
+        for arch, cfg in zip((first, "llama"), configs(z)):
             tensors = dict(random_tensors(cfg, 0, torch.bfloat16, device="cuda:0"))
             spec = model_from_tensors(cfg, tensors, "bfloat16", "cuda:0")
             del tensors
@@ -352,8 +419,8 @@ def compare_main(args) -> int:
             pre = prefill_times(spec, ec, COMPARE_VOCAB)
             fam = {k: {kk: {"calls": c, "ms": round(ms, 4)} for kk, (c, ms) in family_profile(spec, COMPARE_VOCAB, k).items()}
                    for k in ("prefill", "decode")}
-            work = {"prefill": (tolanex_work if arch == "tolanex" else llama_work)(z, PREFILL_TOKENS, PREFILL_TOKENS, False),
-                    "decode": (tolanex_work if arch == "tolanex" else llama_work)(z, 8, 1024, True)}
+            work = {"prefill": (first_work if arch == first else llama_work)(z, PREFILL_TOKENS, PREFILL_TOKENS, False),
+                    "decode": (first_work if arch == first else llama_work)(z, 8, 1024, True)}
             res[arch] = {"decode_tokens_per_s": round(8 * steps * 1e3 / dec["dev_ms"], 1),
                          "decode_ms_per_step": round(dec["dev_ms"] / steps, 4),
                          "decode_e2e_tokens_per_s": round(8 * steps * 1e3 / dec["wall_ms"], 1),
@@ -493,10 +560,11 @@ def main() -> int:
                          "'native' this engine's kernels only, 'library' the library wherever it can stand")
     ap.add_argument("--only", default="all", choices=["all", "prefill"],
                     help="'prefill': run only the 2,048-token prefill step and print its numbers (for profiling)")
-    ap.add_argument("--compare", default="", choices=["", "tolanex"],
-                    help="'tolanex': instead of the default workload, prefill and decode of the Tolanex design beside "
+    ap.add_argument("--compare", default="", choices=["", "tolanex", "bifatar"],
+                    help="'tolanex' | 'bifatar': instead of the default workload, prefill and decode of that design beside "
                          "the Llama decoder at equal sizes, with device time per kernel family")
-    ap.add_argument("--size", default="all", choices=["all"] + sorted(COMPARE_SIZES), help="with --compare: one size only")
+    ap.add_argument("--size", default="all", choices=["all"] + sorted(COMPARE_SIZES) + sorted(BIFATAR_SIZES),
+                    help="with --compare: one size only")
     args = ap.parse_args()
 
     if args.impl == "reference":
