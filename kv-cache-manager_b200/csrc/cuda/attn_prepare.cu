@@ -34,20 +34,31 @@ struct AttnPrepareParams {
   int nh, nkv, dk, dv, HD;
 };
 
+__device__ __forceinline__ void store_pair(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void store_pair(bf16* p, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(512)
 attn_prepare_kernel(AttnPrepareParams p) {
-  extern __shared__ float row[];
+  extern __shared__ __align__(16) float row[];                     // the row, then `rot` floats: cosines, sines
   __shared__ float scratch[33];
   pdl_launch_dependents();
   const int r = blockIdx.x, tid = threadIdx.x;
   const int nq = p.nh * p.dk, nk = p.nkv * p.dk, nv = p.nkv * p.dv;
   const int n = nq + nk + nv;
+  float* cs_table = row + n;
   pdl_wait();
-  for (int i = tid; i < n; i += blockDim.x) {
-    float v = p.proj[size_t(r) * p.ldp + i];
-    if (p.bias) v += p.bias[i];
-    row[i] = v;
+  const float* src = p.proj + size_t(r) * p.ldp;
+  if ((n & 3) == 0 && (p.ldp & 3) == 0 && (reinterpret_cast<uintptr_t>(p.proj) & 15) == 0) {
+    for (int i = 4 * tid; i < n; i += 4 * blockDim.x) {
+      float4 v = *reinterpret_cast<const float4*>(src + i);
+      if (p.bias) { v.x += p.bias[i]; v.y += p.bias[i + 1]; v.z += p.bias[i + 2]; v.w += p.bias[i + 3]; }
+      *reinterpret_cast<float4*>(row + i) = v;
+    }
+  } else {
+    for (int i = tid; i < n; i += blockDim.x) row[i] = src[i] + (p.bias ? p.bias[i] : 0.f);
   }
   __syncthreads();
   if (p.wq) {
@@ -62,16 +73,17 @@ attn_prepare_kernel(AttnPrepareParams p) {
     __syncthreads();
   }
   if (p.rot > 0) {
+    // the row's cosines and sines once (they are the same for every head), then the pairs of all heads
     const int half = p.rot / 2;
     const float pos = float(p.positions[r]);
+    for (int j = tid; j < half; j += blockDim.x) sincosf(pos * p.inv_freq[j], &cs_table[half + j], &cs_table[j]);
+    __syncthreads();
     const int pairs = (p.nh + p.nkv) * half;
     for (int i = tid; i < pairs; i += blockDim.x) {
       const int head = i / half, j = i - head * half;
-      float sn, cs;
-      sincosf(pos * p.inv_freq[j], &sn, &cs);
       float* x = row + size_t(head) * p.dk;           // q heads, then k heads: both are dk wide and adjacent
       float a, b;
-      rotate_pair(x[j], x[j + half], cs, sn, a, b);
+      rotate_pair(x[j], x[j + half], cs_table[j], cs_table[half + j], a, b);
       x[j] = a;
       x[j + half] = b;
     }
@@ -98,10 +110,13 @@ attn_prepare_kernel(AttnPrepareParams p) {
     }
     __syncthreads();
   }
+  // a warp per head, two neighbouring elements a lane (HD is even: a multiple of 8)
+  const int lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
   T* qo = reinterpret_cast<T*>(p.q_out) + size_t(r) * p.nh * p.HD;
-  for (int i = tid; i < p.nh * p.HD; i += blockDim.x) {
-    const int head = i / p.HD, d = i - head * p.HD;
-    stf(qo + i, d < p.dk ? row[head * p.dk + d] : 0.f);
+  for (int head = warp; head < p.nh; head += nwarps) {
+    const float* x = row + size_t(head) * p.dk;
+    for (int d = 2 * lane; d < p.HD; d += 64)
+      store_pair(qo + size_t(head) * p.HD + d, d < p.dk ? x[d] : 0.f, d + 1 < p.dk ? x[d + 1] : 0.f);
   }
   const int slot = p.slot_mapping ? p.slot_mapping[r] : -1;
   if (slot < 0) return;
@@ -110,24 +125,28 @@ attn_prepare_kernel(AttnPrepareParams p) {
   const size_t head_stride = size_t(p.block_size) * p.HD;
   T* kc = reinterpret_cast<T*>(p.k_cache) + base;
   T* vc = reinterpret_cast<T*>(p.v_cache) + base;
-  for (int i = tid; i < p.nkv * p.HD; i += blockDim.x) {
-    const int head = i / p.HD, d = i - head * p.HD;
-    stf(kc + head * head_stride + d, d < p.dk ? row[nq + head * p.dk + d] : 0.f);
-    stf(vc + head * head_stride + d, d < p.dv ? row[nq + nk + head * p.dv + d] : 0.f);
+  for (int hh = warp; hh < 2 * p.nkv; hh += nwarps) {
+    const bool is_v = hh >= p.nkv;
+    const int head = is_v ? hh - p.nkv : hh, width = is_v ? p.dv : p.dk;
+    const float* x = is_v ? row + nq + nk + size_t(head) * p.dv : row + nq + size_t(head) * p.dk;
+    T* dst = (is_v ? vc : kc) + head * head_stride;
+    for (int d = 2 * lane; d < p.HD; d += 64) store_pair(dst + d, d < width ? x[d] : 0.f, d + 1 < width ? x[d + 1] : 0.f);
   }
 }
 
 template <typename T>
 int launch_attn_prepare(const AttnPrepareParams& p, int rows, cudaStream_t s) {
   if (rows == 0) return 0;
-  if (p.rot % 2 || p.rot > p.dk || p.HD < p.dk || p.HD < p.dv) return KVCM_ERR_UNSUPPORTED;
-  const size_t smem = size_t(p.nh * p.dk + p.nkv * p.dk + p.nkv * p.dv) * sizeof(float);
+  if (p.rot % 2 || p.rot > p.dk || p.HD < p.dk || p.HD < p.dv || p.HD % 2) return KVCM_ERR_UNSUPPORTED;
+  const size_t smem = size_t(p.nh * p.dk + p.nkv * p.dk + p.nkv * p.dv + p.rot) * sizeof(float);
   if (smem > 200 * 1024) return KVCM_ERR_UNSUPPORTED;
   if (smem > 48 * 1024) {
     const cudaError_t e = cudaFuncSetAttribute(attn_prepare_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return int(e);
   }
-  return pdl_launch(attn_prepare_kernel<T>, dim3(rows), dim3(256), smem, s, p);
+  // a row of a few thousand elements is a chain of short passes: more threads, fewer turns each
+  const int threads = (p.nh + 2 * p.nkv) * p.HD >= 2048 ? 512 : 256;
+  return pdl_launch(attn_prepare_kernel<T>, dim3(rows), dim3(threads), smem, s, p);
 }
 
 }  // namespace kvcm

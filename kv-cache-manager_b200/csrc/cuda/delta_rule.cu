@@ -251,6 +251,7 @@ delta_scan_kernel(const ScanArgs A) {
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     __syncthreads();                                   // this tile has landed; the other buffer has been consumed
     if (t0 + TT < n) stage(buf ^ 1, t0 + TT);
+#pragma unroll(MODE == kScanLinear ? 4 : 1)
     for (int t = 0; t < nt; ++t) {
       const float g = CHD ? 1.f : gs[buf][t], beta = bs[buf][t];
       float kt[NI], qt[NI];
@@ -442,7 +443,11 @@ static int launch_scan(const ScanArgs& A, int rows, int seqs, cudaStream_t s) {
   else if (dk <= 16) KVCM_SCAN(4, 4, 16);
   else if (dk <= 32) KVCM_SCAN(4, 8, 16);
   else if (dk <= 64) { if (single_rows) KVCM_SCAN(4, 16, 16); else KVCM_SCAN(8, 8, 16); }
-  else if (dk <= 128) { if (single_rows) KVCM_SCAN(4, 32, TT_LONG); else KVCM_SCAN(8, 16, TT_LONG); }
+  else if (dk <= 128) {
+    if (single_rows) KVCM_SCAN(4, 32, TT_LONG);
+    else if constexpr (MODE == kScanLinear) KVCM_SCAN(16, 8, 16);   // no chain through the step: more, shorter threads
+    else KVCM_SCAN(8, 16, TT_LONG);
+  }
   else KVCM_SCAN(8, 32, TT_LONGEST);
 #undef KVCM_SCAN
 #undef KVCM_SCAN_C
@@ -493,7 +498,7 @@ delta_prepare_channel_kernel(float* __restrict__ qkv, int channels, const T* __r
   const int row = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const float qscale = 1.f / sqrtf(float(dk));
-  for (int hh = warp; hh < 2 * qk_heads; hh += nwarps) {
+  for (int hh = blockIdx.y * nwarps + warp; hh < 2 * qk_heads; hh += gridDim.y * nwarps) {
     float* p = qkv + size_t(row) * channels + size_t(hh) * dk;
     float ss = 0.f;
     for (int i = lane; i < dk; i += 32) ss += p[i] * p[i];
@@ -502,9 +507,9 @@ delta_prepare_channel_kernel(float* __restrict__ qkv, int channels, const T* __r
     if (hh < qk_heads) inv *= qscale;
     for (int i = lane; i < dk; i += 32) p[i] *= inv;
   }
-  for (int h = threadIdx.x; h < heads; h += blockDim.x)
+  for (int h = blockIdx.y * blockDim.x + threadIdx.x; h < heads; h += gridDim.y * blockDim.x)
     beta[size_t(row) * heads + h] = 1.f / (1.f + expf(-ldf(b + size_t(row) * ldb + h)));
-  for (int i = threadIdx.x; i < heads * dk; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < heads * dk; i += gridDim.y * blockDim.x) {
     const float z = a[size_t(row) * heads * dk + i] + dt_bias[i];
     const float sp = z > 20.f ? z : log1pf(expf(z));
     a[size_t(row) * heads * dk + i] = expf(-expf(a_log[i / dk]) * sp);
@@ -568,6 +573,47 @@ group_rms_gate_kernel(const float* __restrict__ o, const T* __restrict__ z, int 
   }
 }
 
+// The same for groups of more than 256 elements: one block per (row, group), so that a long group's
+// loads are in flight together instead of one warp walking it.
+template <typename T>
+__global__ void __launch_bounds__(256)
+group_rms_gate_wide_kernel(const float* __restrict__ o, const T* __restrict__ z, int ldz, const float* __restrict__ skip,
+                           int lds, const float* __restrict__ skip_coef, int head, const float* __restrict__ w, int wlen,
+                           T* __restrict__ out, int n, int group, int gate_first, int act, float eps) {
+  __shared__ float scratch[33];
+  const int row = blockIdx.x, i0 = blockIdx.y * group;
+  constexpr int kKeep = 8;                                 // values a thread keeps between the two passes
+  float kept[kKeep], gates[kKeep];
+  float ss = 0.f;
+  int c = 0;
+  for (int j = threadIdx.x; j < group; j += blockDim.x, ++c) {
+    const int i = i0 + j;
+    float v = o[size_t(row) * n + i];
+    if (skip) v = fmaf(skip_coef[i / head], skip[size_t(row) * lds + i], v);
+    const float gz = gate_act(ldf(z + size_t(row) * ldz + i), act);
+    if (gate_first) v *= gz;
+    if (c < kKeep) { kept[c] = v; gates[c] = gz; }
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.f / sqrtf(ss / float(group) + eps);
+  c = 0;
+  for (int j = threadIdx.x; j < group; j += blockDim.x, ++c) {
+    const int i = i0 + j;
+    float v, gz;
+    if (c < kKeep) { v = kept[c]; gz = gates[c]; }
+    else {
+      v = o[size_t(row) * n + i];
+      if (skip) v = fmaf(skip_coef[i / head], skip[size_t(row) * lds + i], v);
+      gz = gate_act(ldf(z + size_t(row) * ldz + i), act);
+      if (gate_first) v *= gz;
+    }
+    v = v * inv * w[i % wlen];
+    if (!gate_first) v *= gz;
+    stf(out + size_t(row) * n + i, v);
+  }
+}
+
 template <typename T>
 static int launch_group_rms_gate(const float* o, const void* z, int ldz, const float* skip, int lds, const float* skip_coef,
                                  int head, const float* w, int wlen, void* out, int rows, int n, int group, int gate_first,
@@ -575,6 +621,11 @@ static int launch_group_rms_gate(const float* o, const void* z, int ldz, const f
   if (rows == 0) return 0;
   if (group < 1 || n % group || wlen < 1 || (skip && head < 1)) return KVCM_ERR_UNSUPPORTED;
   const int groups = n / group;
+  if (group > 256 && groups <= 65535) {
+    group_rms_gate_wide_kernel<T><<<dim3(rows, groups), 256, 0, s>>>(o, (const T*)z, ldz, skip, lds, skip_coef, head, w, wlen,
+                                                                      (T*)out, n, group, gate_first, act, eps);
+    return KVCM_LAUNCH_RESULT();
+  }
   group_rms_gate_kernel<T><<<dim3(rows, (groups + 3) / 4), 128, 0, s>>>(o, (const T*)z, ldz, skip, lds, skip_coef, head, w, wlen,
                                                                        (T*)out, n, group, gate_first, act, eps);
   return KVCM_LAUNCH_RESULT();
@@ -596,7 +647,7 @@ KVCM_API int kvcm_delta_prepare_channel_f32(float* qkv, int channels, const void
                                             const float* a_log, const float* dt_bias, int rows, int heads, int qk_heads,
                                             int dk, void* stream) {
   if (rows == 0) return 0;
-  delta_prepare_channel_kernel<float><<<rows, 128, 0, (cudaStream_t)stream>>>(qkv, channels, (const float*)b, ldb, beta, a,
+  delta_prepare_channel_kernel<float><<<dim3(rows, max(1, min(16, (heads * dk + 511) / 512))), 128, 0, (cudaStream_t)stream>>>(qkv, channels, (const float*)b, ldb, beta, a,
                                                                               a_log, dt_bias, heads, qk_heads, dk);
   return KVCM_LAUNCH_RESULT();
 }
@@ -604,7 +655,7 @@ KVCM_API int kvcm_delta_prepare_channel_bf16(float* qkv, int channels, const voi
                                              const float* a_log, const float* dt_bias, int rows, int heads, int qk_heads,
                                              int dk, void* stream) {
   if (rows == 0) return 0;
-  delta_prepare_channel_kernel<bf16><<<rows, 128, 0, (cudaStream_t)stream>>>(qkv, channels, (const bf16*)b, ldb, beta, a,
+  delta_prepare_channel_kernel<bf16><<<dim3(rows, max(1, min(16, (heads * dk + 511) / 512))), 128, 0, (cudaStream_t)stream>>>(qkv, channels, (const bf16*)b, ldb, beta, a,
                                                                              a_log, dt_bias, heads, qk_heads, dk);
   return KVCM_LAUNCH_RESULT();
 }
