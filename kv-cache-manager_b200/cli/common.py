@@ -41,10 +41,31 @@ def _tolanex_mini():
             ]}
 
 
+def _bifatar_mini():
+    """A small Bifatar: windowed attention (values kept), the state-space mixer, attention beside the
+    channel-decay delta rule, windowed attention that mixes the first layer's values."""
+    def attn(window, base):
+        return {"heads": 6, "kv_heads": 2, "dim": 64, "vdim": 64, "scale": 0.1, "rot": {"base": base, "dims": 32},
+                "mask": {"size": window}, "softcap": 25.0, "v_mix": True}
+    dense = {"kind": "dense", "ff": 768}
+    return {"architecture": "Bifatar", "vocab": 1000, "width": 384, "norm": {"eps": 1e-5},
+            "layers": [
+                {"type": "attention", "mixer": attn(200, 10000.0), "mlp": dense},
+                {"type": "mamba2", "mixer": {"heads": 12, "vdim": 64, "state": 64, "groups": 2, "conv": 4, "norm_groups": 2},
+                 "mlp": dense},
+                {"type": "parallel", "mixer": {
+                    "left": {"heads": 6, "kv_heads": 2, "dim": 64, "vdim": 32, "scale": 0.125, "rot": {"base": 500000.0, "dims": 64}},
+                    "right": {"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 96, "conv": 3, "decay_rank": 16, "gate_rank": 24},
+                    "left_scale": 1.0, "right_scale": 0.5}, "mlp": None},
+                {"type": "attention", "mixer": attn(72, 50000.0), "mlp": dense},
+            ]}
+
+
 PRESETS = {
     # name: (config.json keys, seed, norm jitter); keys with "architecture" go through the registry,
     # the others are those of a Llama dense decoder
     "tolanex-mini": (_tolanex_mini(), 4, 0.1),
+    "bifatar-mini": (_bifatar_mini(), 5, 0.1),
     "tiny-a": (dict(vocab_size=256, hidden_size=64, intermediate_size=172, num_hidden_layers=2,
                     num_attention_heads=4, num_key_value_heads=2, head_dim=16, max_position_embeddings=128,
                     rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False), 0, 0.0),

@@ -79,3 +79,17 @@ def test_kvbench_and_kvcorrect_on_the_tolanex_preset():
     assert rc in (0, 2), out[-2000:] + err[-2000:]
     assert "[PASS] alone (scattered pages) = batch" in out and "[PASS] paged = contiguous" in out
     assert "[SKIP] prefix cache" in out
+
+
+def test_kvbench_and_kvcorrect_on_the_bifatar_preset():
+    """A third architecture through the same flags: windowed pages, two kinds of per-request state and
+    values handed from layer to layer, served by the scheduler, and kvcorrect's checks on the cache."""
+    rc, out, err = run("kvbench", "--preset", "bifatar-mini", "--requests", "10", "--rate", "0", "--prompt-len", "60",
+                       "--output-len", "12", "--max-seq-len", "128", "--num-blocks", "48", "--max-num-seqs", "4",
+                       "--max-batched-tokens", "96", "--warmup", "1")
+    assert rc == 0, err[-2000:]
+    assert "completed 10/10" in out
+    rc, out, err = run("kvcorrect", "--preset", "bifatar-mini", "--steps", "8", "--prompts", "3", "--prompt-len", "40")
+    assert rc in (0, 2), out[-2000:] + err[-2000:]
+    assert "[PASS] alone (scattered pages) = batch" in out and "[PASS] paged = contiguous" in out
+    assert "[SKIP] prefix cache" in out
