@@ -73,6 +73,33 @@ delta_conv_state_kernel(const T* __restrict__ proj, int ldp, int taps, float* __
   }
 }
 
+// Both in one, for a step in which every request brings exactly one row (row == request): a thread owns one
+// (request, channel), reads the kept inputs, writes the output and moves the state on.
+template <typename T>
+__global__ void __launch_bounds__(256)
+delta_conv_single_kernel(const T* __restrict__ proj, int ldp, const float* __restrict__ conv_w, int taps,
+                         float* __restrict__ state, long long state_stride, long long conv_off,
+                         const int* __restrict__ seq_q_start, const int* __restrict__ seq_state_slot,
+                         float* __restrict__ out, int channels, const float* __restrict__ bias) {
+  const int s = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  const int slot = seq_state_slot[s], row = seq_q_start[s];
+  const float cur = ldf(proj + size_t(row) * ldp + c);
+  float acc = bias ? bias[c] : 0.f;                   // summed in the order of the taps, as the general kernel does
+  if (slot >= 0) {
+    float* kept = state + slot * state_stride + conv_off;
+    for (int j = 0; j < taps - 1; ++j) {
+      const float v = kept[size_t(j) * channels + c];
+      acc = fmaf(conv_w[size_t(c) * taps + j], v, acc);
+      if (j > 0) kept[size_t(j - 1) * channels + c] = v;
+    }
+    if (taps > 1) kept[size_t(taps - 2) * channels + c] = cur;
+  }
+  acc = fmaf(conv_w[size_t(c) * taps + taps - 1], cur, acc);
+  out[size_t(row) * channels + c] = silu_f(acc);
+}
+
 // ------------------------------------------------------------ unit vectors, step sizes, decays
 // qkv[row]: the first 2 * qk_heads heads of dk (queries, then keys) become unit vectors
 // (x / sqrt(sum x^2 + 1e-6); queries also times dk^-1/2).  ba[row] = [b | a] becomes [beta | g].
@@ -168,8 +195,14 @@ delta_scan_kernel(const ScanArgs A) {
   __shared__ __align__(16) float gds[CHD ? 2 : 1][CHD ? TT : 1][CHD ? DKP : 4];
   const int s = blockIdx.z, head = blockIdx.y;
   const int slot = seq_state_slot[s];
-  if (slot < 0) return;
   const int q0 = seq_q_start[s], n = seq_q_len[s];
+  if (slot < 0) {                                       // a padding entry: its rows of the output are zeros
+    for (int idx = threadIdx.x; idx < n * DR_COLS; idx += blockDim.x) {
+      const int c = blockIdx.x * DR_COLS + idx % DR_COLS;
+      if (c < dv) out[size_t(q0 + idx / DR_COLS) * heads * dv + size_t(head) * dv + c] = 0.f;
+    }
+    return;
+  }
   const int qk_head = head / (heads / qk_heads);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int col_local = warp * CPW + (lane % CPW);
@@ -365,6 +398,11 @@ int launch_delta_conv(const void* proj, int ldp, const float* conv_w, int taps, 
   if (rows == 0) return 0;
   if (taps < 1) return KVCM_ERR_UNSUPPORTED;
   const int by = (channels + 255) / 256;
+  if (rows == seqs) {                            // every request brings one row: rows and requests coincide
+    delta_conv_single_kernel<T><<<dim3(rows, by), 256, 0, s>>>((const T*)proj, ldp, conv_w, taps, state, state_stride, conv_off,
+                                                               seq_q_start, seq_state_slot, out, channels, bias);
+    return KVCM_LAUNCH_RESULT();
+  }
   delta_conv_kernel<T><<<dim3(rows, by), 256, 0, s>>>((const T*)proj, ldp, conv_w, taps, state, state_stride, conv_off,
                                                       row_seq, seq_q_start, seq_state_slot, out, channels, bias);
   int rc = KVCM_LAUNCH_RESULT();

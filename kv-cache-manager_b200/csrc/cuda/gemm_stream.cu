@@ -102,6 +102,8 @@ struct StreamParams {
   // SCALED: the sums of row m are multiplied by rsqrt(sum over t of ss_in[t][m] / K + eps) before the
   // epilogue (ss_in [ss_tiles][kNormRows] as kResidual leaves it)
   const float* ss_in; int ss_tiles; float eps;
+  // kStore: 1 = the stored value is max(y, 0)^2 of the rounded sum y (an ungated feed-forward's activation)
+  int relu_sq;
 };
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -485,7 +487,14 @@ gemm_stream_kernel(StreamParams p) {
       for (int e = tid; e < 16 * MB; e += kConsumerThreads) {
         const int m = e >> 4, r = e & 15;
         const int n = row_in(base, r);
-        if (n < p.N && m < p.M) stf(Y + size_t(m) * p.ldy + n, total_of(r, m));
+        if (n < p.N && m < p.M) {
+          float v = total_of(r, m);
+          if (p.relu_sq) {                                       // as the separate kernel: round, clamp, square
+            v = fmaxf(Store<OutT>::round(v), 0.f);
+            v *= v;
+          }
+          stf(Y + size_t(m) * p.ldy + n, v);
+        }
       }
     } else {
       bf16* Y = reinterpret_cast<bf16*>(p.Y);
@@ -629,6 +638,20 @@ KVCM_API int kvcm_gemm_stream_bf16(const void* X, const void* W, void* Y, int M,
   cudaStream_t s = (cudaStream_t)stream;
   if (M <= 8) return out_f32 ? launch_stream<1, float, kStore>(p, sm_count, s) : launch_stream<1, bf16, kStore>(p, sm_count, s);
   return out_f32 ? launch_stream<2, float, kStore>(p, sm_count, s) : launch_stream<2, bf16, kStore>(p, sm_count, s);
+}
+
+// The plain product with the squared ReLU applied to the rounded sums: Y = bfloat16(max(bfloat16(X * W^T), 0)^2).
+KVCM_API int kvcm_gemm_stream_relu_sq_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int ldx,
+                                           int ldw, int ldy, int sm_count, void* stream) {
+  if (M == 0 || N == 0) return 0;
+  if (!stream_ok(M, N, K, sm_count, true) || (ldw % 8) || (ldx % 8)) return KVCM_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(X) & 15)) return KVCM_ERR_UNSUPPORTED;
+  StreamParams p = {};
+  p.W = (const bf16*)W; p.N = N; p.K = K; p.ldw = ldw; p.X = (const bf16*)X; p.ldx = ldx; p.M = M;
+  p.Y = Y; p.ldy = ldy; p.relu_sq = 1;
+  p.pair_blocks = 1; p.group_stride = 16; p.pair_offset = 8;
+  cudaStream_t s = (cudaStream_t)stream;
+  return M <= 8 ? launch_stream<1, bf16, kStore>(p, sm_count, s) : launch_stream<2, bf16, kStore>(p, sm_count, s);
 }
 
 // The product that ends a sublayer: resid[M, N] (float, in place) += round_bf16(X * W^T);

@@ -560,6 +560,19 @@ def gemm_stream(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
     _check(rc, "gemm_stream", f"(M={M}, N={N}, K={K})")
 
 
+def gemm_stream_relu_sq(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
+    """y = max(bfloat16(x @ w^T), 0)^2 in bfloat16: the streaming product of ``gemm_stream`` with the
+    activation of an ungated feed-forward in its epilogue (the same roundings as product, then ``relu_sq``)."""
+    _cuda(x, w, y)
+    M, K = x.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and y.shape == (M, N) and x.dtype == w.dtype == y.dtype == torch.bfloat16
+          and x.stride(1) == 1 and w.stride(1) == 1 and y.stride(1) == 1, "gemm_stream_relu_sq: bfloat16 [M,K] x [N,K]")
+    rc = _lib().kvcm_gemm_stream_relu_sq_bf16(_p(x), _p(w), _p(y), M, N, K, x.stride(0), w.stride(0), y.stride(0),
+                                              sm_count(x.device), _stream())
+    _check(rc, "gemm_stream", f"(M={M}, N={N}, K={K}, relu_sq)")
+
+
 def stream_test_hooks(wait_limit_ns: int = 0, skip_stage: int = -1) -> None:
     """For tests of the failure path: the streaming product's wait limit (0 = its default) and a
     stage of every block whose copy is left out (-1 = none), so that a wait runs out."""
@@ -963,9 +976,9 @@ def delta_conv(proj: torch.Tensor, conv_w: torch.Tensor, state: torch.Tensor, co
     fn = getattr(_lib(), "kvcm_delta_conv_" + _suffix(proj))
     _check(fn(_p(proj), proj.stride(0), _p(conv_w), taps, _p(state), _ll(state.stride(0)), _ll(conv_off), _p(ctx.row_seq),
               _p(ctx.seq_q_start), _p(ctx.seq_q_len), _p(ctx.seq_state_slot), _p(out), T, ctx.seqs, C, _p(bias), _stream()), "delta_conv")
-    if taps > 1:
+    if taps > 1 and T != ctx.seqs:
         global _launches
-        _launches += 1                      # the state update
+        _launches += 1                      # the state update (a kernel of its own unless every request brings one row)
 
 
 def delta_prepare(qkv: torch.Tensor, ba: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,

@@ -64,7 +64,7 @@ class GatedDeltaMixer(Mixer):
         qkv = torch.empty((M, C), dtype=torch.float32, device=h.device)
         K.delta_conv(proj, self._f32["conv"], site.state, H * self.dk * self.dv, ctx, qkv)
         K.delta_prepare(qkv, ba, self._f32["A_log"], self._f32["dt_bias"], H, self.qk_heads, self.dk)
-        o = torch.zeros((M, H * self.dv), dtype=torch.float32, device=h.device)   # padding rows stay zero
+        o = torch.empty((M, H * self.dv), dtype=torch.float32, device=h.device)   # (the scan zeroes padding rows)
         K.delta_scan(qkv, ba, site.state, ctx, o, H, self.qk_heads, self.dk, self.dv)
         gated = torch.empty((M, H * self.dv), dtype=h.dtype, device=h.device)
         K.gated_rms(o, proj[:, C:], self._f32["norm"], gated, H, self.dv, self.norm_eps)
@@ -149,7 +149,7 @@ class ChannelDecayDeltaMixer(Mixer):
         beta = torch.empty((T, H), dtype=torch.float32, device=h.device)
         K.delta_prepare_channel(qkv, low[:, ra + rg:ra + rg + H], beta, decay, self._f32["A_log"], self._f32["dt_bias"],
                                 H, self.qk_heads, self.dk)
-        o = torch.zeros((T, H * self.dv), dtype=torch.float32, device=h.device)       # padding rows stay zero
+        o = torch.empty((T, H * self.dv), dtype=torch.float32, device=h.device)       # (the scan zeroes padding rows)
         K.state_scan(K.SCAN_DELTA_CHANNEL, qkv, (0, self.qk_heads * self.dk, 2 * self.qk_heads * self.dk), beta, None, decay,
                      site.state, ctx, o, H, self.qk_heads, self.dk, self.dv)
         gated = torch.empty((T, H * self.dv), dtype=h.dtype, device=h.device)

@@ -8,7 +8,7 @@ import torch
 
 from ..kernels import library as K
 from .base import FEED_FORWARDS, FeedForward, StepContext
-from .linear import Linear, TCGEN05_GATED_MAX_HIDDEN, TCGEN05_MIN_ROWS, tiles_fill_well
+from .linear import Linear, STREAM_MAX_BYTES, TCGEN05_GATED_MAX_HIDDEN, TCGEN05_MIN_ROWS, tiles_fill_well
 
 
 @FEED_FORWARDS.register("gated_mlp")
@@ -64,6 +64,16 @@ class DenseMLP(FeedForward):
         self.down = self.add_child("down", Linear(intermediate, hidden, intermediate ** -0.5))
 
     def forward(self, h: torch.Tensor, ctx: StepContext, out_dtype=None) -> torch.Tensor:
-        z = self.up.forward(h, ctx)
-        K.relu_sq(z, z)
+        w = self.up.param("weight")
+        M = h.shape[0]
+        # A handful of rows (decode): the up product applies the activation in its epilogue (the same
+        # roundings as the two separate kernels), where `matmul_nt` would take the streaming kernel anyway.
+        if (h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and ctx.options.get("gemm", "auto") in ("auto", "native")
+                and ctx.options.get("fuse", True) and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0
+                and (M <= 8 or w.numel() * 2 <= STREAM_MAX_BYTES) and K.stream_gemm_supported(M, self.intermediate, h.shape[1])):
+            z = torch.empty((M, self.intermediate), dtype=h.dtype, device=h.device)
+            K.gemm_stream_relu_sq(h, w, z)
+        else:
+            z = self.up.forward(h, ctx)
+            K.relu_sq(z, z)
         return self.down.forward(z, ctx, out_dtype)

@@ -66,7 +66,7 @@ class Mamba2Mixer(Mixer):
         K.delta_conv(proj[:, inner:inner + C], f["conv"], site.state, H * self.state * self.vdim, ctx, xbc, f["conv_bias"])
         steps = torch.empty((T, 2 * H), dtype=torch.float32, device=h.device)            # [dt | decay]
         K.ssm_prepare(proj[:, inner + C:], f["A_log"], f["dt_bias"], steps, H)
-        y = torch.zeros((T, inner), dtype=torch.float32, device=h.device)                # padding rows stay zero
+        y = torch.empty((T, inner), dtype=torch.float32, device=h.device)                # (the scan zeroes padding rows)
         K.state_scan(K.SCAN_LINEAR, xbc, (inner + GN, inner, 0), steps[:, :H], steps[:, H:], None, site.state, ctx, y,
                      H, self.groups, self.state, self.vdim)
         gated = torch.empty((T, inner), dtype=h.dtype, device=h.device)

@@ -348,6 +348,26 @@ def test_tanh_norm_kernel_with_three_pending_outputs():
             assert torch.equal(xs2, x) and torch.equal(out2, out[[7, 2]])
 
 
+def test_squared_relu_in_the_streaming_product():
+    """The up product of a decode step applies the activation in its epilogue: the same bits as the product
+    followed by the activation kernel."""
+    from kvcm.kernels import library as K
+    g = torch.Generator().manual_seed(2)
+    for M, N, Kd in ((1, 320, 128), (8, 1000, 256), (13, 64, 512)):
+        x = torch.randn(M, Kd, generator=g).to(torch.bfloat16).cuda()
+        w = (torch.randn(N, Kd, generator=g) * Kd ** -0.5).to(torch.bfloat16).cuda()
+        if not K.stream_gemm_supported(M, N, Kd):
+            continue
+        y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        K.gemm_stream(x, w, y)
+        K.relu_sq(y, y)
+        z = torch.empty_like(y)
+        K.gemm_stream_relu_sq(x, w, z)
+        assert torch.equal(y, z)
+        ref = torch.relu(x.double() @ w.double().T) ** 2
+        assert (z.double() - ref).abs().max().item() < 0.05 * max(1.0, ref.abs().max().item())
+
+
 def test_capped_attention_with_a_sink_in_every_kernel():
     """The tensor-core attention kernels (decode in one block, split over a cluster, split through scratch
     memory; prefill) against the plain kernel, with a cap, a sink and a window."""
