@@ -42,13 +42,20 @@ __device__ __forceinline__ void store_pair(bf16* p, float a, float b) {
 template <typename T>
 __global__ void __launch_bounds__(512)
 attn_prepare_kernel(AttnPrepareParams p) {
-  extern __shared__ __align__(16) float row[];                     // the row, then `rot` floats: cosines, sines
+  extern __shared__ __align__(16) float row[];       // the row, then `rot` floats: cosines, sines
   __shared__ float scratch[33];
   pdl_launch_dependents();
   const int r = blockIdx.x, tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
   const int nq = p.nh * p.dk, nk = p.nkv * p.dk, nv = p.nkv * p.dv;
   const int n = nq + nk + nv;
+  const int half = p.rot / 2;
   float* cs_table = row + n;
+  // the row's cosines and sines depend on nothing the step computes: before the wait
+  if (half > 0) {
+    const float pos = float(p.positions[r]);
+    for (int j = tid; j < half; j += blockDim.x) sincosf(pos * p.inv_freq[j], &cs_table[half + j], &cs_table[j]);
+  }
   pdl_wait();
   const float* src = p.proj + size_t(r) * p.ldp;
   if ((n & 3) == 0 && (p.ldp & 3) == 0 && (reinterpret_cast<uintptr_t>(p.proj) & 15) == 0) {
@@ -61,76 +68,69 @@ attn_prepare_kernel(AttnPrepareParams p) {
     for (int i = tid; i < n; i += blockDim.x) row[i] = src[i] + (p.bias ? p.bias[i] : 0.f);
   }
   __syncthreads();
-  if (p.wq) {
+  float iq = 1.f, ik = 1.f;
+  if (p.wq) {                                        // the norm over the whole projections: the block's only reductions
     float sq = 0.f, sk = 0.f;
     for (int i = tid; i < nq; i += blockDim.x) sq = fmaf(row[i], row[i], sq);
     for (int i = tid; i < nk; i += blockDim.x) sk = fmaf(row[nq + i], row[nq + i], sk);
     sq = block_sum(sq, scratch);
     sk = block_sum(sk, scratch);
-    const float iq = 1.f / sqrtf(sq / float(nq) + p.eps), ik = 1.f / sqrtf(sk / float(nk) + p.eps);
-    for (int i = tid; i < nq; i += blockDim.x) row[i] = row[i] * iq * p.wq[i];
-    for (int i = tid; i < nk; i += blockDim.x) row[nq + i] = row[nq + i] * ik * p.wk[i];
-    __syncthreads();
+    iq = 1.f / sqrtf(sq / float(nq) + p.eps);
+    ik = 1.f / sqrtf(sk / float(nk) + p.eps);
   }
-  if (p.rot > 0) {
-    // the row's cosines and sines once (they are the same for every head), then the pairs of all heads
-    const int half = p.rot / 2;
-    const float pos = float(p.positions[r]);
-    for (int j = tid; j < half; j += blockDim.x) sincosf(pos * p.inv_freq[j], &cs_table[half + j], &cs_table[j]);
-    __syncthreads();
-    const int pairs = (p.nh + p.nkv) * half;
-    for (int i = tid; i < pairs; i += blockDim.x) {
-      const int head = i / half, j = i - head * half;
-      float* x = row + size_t(head) * p.dk;           // q heads, then k heads: both are dk wide and adjacent
-      float a, b;
-      rotate_pair(x[j], x[j + half], cs_table[j], cs_table[half + j], a, b);
-      x[j] = a;
-      x[j + half] = b;
-    }
-    __syncthreads();
-  }
-  if (p.head_norm) {
-    const int lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
-    for (int head = warp; head < p.nh + p.nkv; head += nwarps) {
-      float* x = row + size_t(head) * p.dk;
-      float ss = 0.f;
-      for (int i = lane; i < p.dk; i += 32) ss = fmaf(x[i], x[i], ss);
-      ss = warp_sum(ss);
-      const float inv = 1.f / sqrtf(ss / float(p.dk) + p.eps);
-      for (int i = lane; i < p.dk; i += 32) x[i] *= inv;
-    }
-    __syncthreads();
-  }
-  if (p.v_keep || p.v_first) {
-    const float lam = p.v_first ? p.lambda[0] : 0.f;
-    for (int i = tid; i < nv; i += blockDim.x) {
-      const float v = row[nq + nk + i];
-      if (p.v_keep) p.v_keep[size_t(r) * nv + i] = v;
-      if (p.v_first) row[nq + nk + i] = (1.f - lam) * v + lam * p.v_first[size_t(r) * nv + i];
-    }
-    __syncthreads();
-  }
-  // a warp per head, two neighbouring elements a lane (HD is even: a multiple of 8)
-  const int lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
-  T* qo = reinterpret_cast<T*>(p.q_out) + size_t(r) * p.nh * p.HD;
-  for (int head = warp; head < p.nh; head += nwarps) {
-    const float* x = row + size_t(head) * p.dk;
-    for (int d = 2 * lane; d < p.HD; d += 64)
-      store_pair(qo + size_t(head) * p.HD + d, d < p.dk ? x[d] : 0.f, d + 1 < p.dk ? x[d + 1] : 0.f);
-  }
+  // From here on a head is one warp's business: whole-projection scale, rotation, per-head norm, value
+  // mixing and the store of that head need nothing of another head (two neighbouring elements a lane).
   const int slot = p.slot_mapping ? p.slot_mapping[r] : -1;
-  if (slot < 0) return;
-  const int page = slot / p.block_size, off = slot - page * p.block_size;
+  const int page = slot >= 0 ? slot / p.block_size : 0, off = slot >= 0 ? slot - page * p.block_size : 0;
   const size_t base = (size_t(page) * p.nkv * p.block_size + off) * p.HD;
   const size_t head_stride = size_t(p.block_size) * p.HD;
-  T* kc = reinterpret_cast<T*>(p.k_cache) + base;
-  T* vc = reinterpret_cast<T*>(p.v_cache) + base;
-  for (int hh = warp; hh < 2 * p.nkv; hh += nwarps) {
-    const bool is_v = hh >= p.nkv;
-    const int head = is_v ? hh - p.nkv : hh, width = is_v ? p.dv : p.dk;
-    const float* x = is_v ? row + nq + nk + size_t(head) * p.dv : row + nq + size_t(head) * p.dk;
-    T* dst = (is_v ? vc : kc) + head * head_stride;
-    for (int d = 2 * lane; d < p.HD; d += 64) store_pair(dst + d, d < width ? x[d] : 0.f, d + 1 < width ? x[d + 1] : 0.f);
+  const float lam = p.v_first ? p.lambda[0] : 0.f;
+  for (int u = warp; u < p.nh + 2 * p.nkv; u += nwarps) {
+    if (u < p.nh + p.nkv) {                          // a query or key head
+      const bool is_q = u < p.nh;
+      float* x = row + size_t(u) * p.dk;             // q heads, then k heads: both dk wide and adjacent
+      if (p.wq) {
+        const float inv = is_q ? iq : ik;
+        const float* w = is_q ? p.wq + size_t(u) * p.dk : p.wk + size_t(u - p.nh) * p.dk;
+        for (int i = lane; i < p.dk; i += 32) x[i] = x[i] * inv * w[i];
+        __syncwarp();
+      }
+      for (int j = lane; j < half; j += 32) {
+        float a, b;
+        rotate_pair(x[j], x[j + half], cs_table[j], cs_table[half + j], a, b);
+        x[j] = a;
+        x[j + half] = b;
+      }
+      __syncwarp();
+      float inv = 1.f;
+      if (p.head_norm) {
+        float ss = 0.f;
+        for (int i = lane; i < p.dk; i += 32) ss = fmaf(x[i], x[i], ss);
+        ss = warp_sum(ss);
+        inv = 1.f / sqrtf(ss / float(p.dk) + p.eps);
+      }
+      T* dst;
+      if (is_q) dst = reinterpret_cast<T*>(p.q_out) + (size_t(r) * p.nh + u) * p.HD;
+      else if (slot >= 0) dst = reinterpret_cast<T*>(p.k_cache) + base + (u - p.nh) * head_stride;
+      else continue;
+      for (int d = 2 * lane; d < p.HD; d += 64)
+        store_pair(dst + d, d < p.dk ? x[d] * inv : 0.f, d + 1 < p.dk ? x[d + 1] * inv : 0.f);
+    } else {                                         // a value head
+      const int head = u - p.nh - p.nkv;
+      float* x = row + nq + nk + size_t(head) * p.dv;
+      const size_t at = size_t(r) * nv + size_t(head) * p.dv;
+      if (p.v_keep || p.v_first) {
+        for (int i = lane; i < p.dv; i += 32) {
+          const float v = x[i];
+          if (p.v_keep) p.v_keep[at + i] = v;
+          if (p.v_first) x[i] = (1.f - lam) * v + lam * p.v_first[at + i];
+        }
+        __syncwarp();
+      }
+      if (slot < 0) continue;
+      T* dst = reinterpret_cast<T*>(p.v_cache) + base + head * head_stride;
+      for (int d = 2 * lane; d < p.HD; d += 64) store_pair(dst + d, d < p.dv ? x[d] : 0.f, d + 1 < p.dv ? x[d + 1] : 0.f);
+    }
   }
 }
 
