@@ -5,7 +5,7 @@
 // that the fast kernels are checked against.  A row's result depends only on its own position,
 // its keys and the window, never on the batch around it.
 // Optional: scores capped as cap * tanh(score / cap); a sink per head, one more term exp(sink) in
-// the softmax's denominator that has no key and no value (the running maximum starts at the sink
+// the softmax's denominator with neither a key nor a value behind it (the running maximum starts at the sink
 // with a sum of one and an empty accumulator).
 //
 // Arithmetic as the reference's kernel (src/cuda/paged_attention.cu:80-182): q is scaled first,

@@ -9,7 +9,7 @@
 //        (i, i + rot/2), angle = position * inv_freq[i]   (rot == 0: none)
 //   4. norm per head, without weights (optional):  x <- x / sqrt(mean_head(x^2) + eps)
 //   5. values: `v_keep` (optional, float [rows, nkv*dv]) receives v as projected;
-//        `v_first` (optional, the same layout) mixes:  v <- (1 - lambda) v + lambda v_first
+//        `v_first` (optional, the same layout) mixes:  v <- v + lambda (v_first - v), evaluated as (1 - lambda) v + lambda v_first
 //   6. q goes to q_out [rows, nh*HD] in the storage type, k and v to the row's page slot
 //        [pages, nkv, page, HD]; HD >= max(dk, dv), elements beyond a head's own size are zero
 //        (zeros add nothing to a score, and the attention output's columns beyond dv stay zero).

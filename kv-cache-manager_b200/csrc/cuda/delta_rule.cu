@@ -152,7 +152,7 @@ __device__ __forceinline__ void dr_copy16(float* dst, const float* src, bool ok)
 //
 // MODE says which recurrence runs (the staging, the state and the split over blocks are the same):
 //   kScanDelta        S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q     one decay g per head
-//   kScanDeltaChannel the same with one decay per head AND key channel: row i of S is scaled by gd[i]
+//   kScanDeltaChannel the same with channel-wise decays: row i of a head's S is scaled by gd[i]
 //   kScanLinear       S <- g S + k (beta v)^T;  o = S^T q        (no correction by the state's own
 //                     read-out: the selective state-space recurrence with k = B, q = C, beta = dt, v = x)
 // Where q, k and v of a row lie is given by `q_base`, `k_base`, `v_base` (floats from the row's start).
@@ -570,7 +570,7 @@ ssm_prepare_kernel(const T* __restrict__ raw, int ld, const float* __restrict__ 
 }
 
 // Norm of the recurrent mixers' outputs in groups of `group` neighbouring elements, with a gate:
-//   v_i   = (o_i + skip_coef[i / head] * skip_i)  [* act(z_i) when the gate comes BEFORE the norm]
+//   v_i   = (o_i + skip_coef[i / head] * skip_i)  [* act(z_i) when the gate is applied ahead of the norm]
 //   out_i = storage( v_i / sqrt(mean_group(v^2) + eps) * w[i % wlen]  [* act(z_i) when it comes after] )
 // act: 0 = SiLU, 1 = sigmoid.  o float [rows, n]; z storage type (row stride ldz); skip float (row stride lds,
 // optional, with one coefficient per `head` elements).  One warp per (row, group).

@@ -3,8 +3,8 @@
 Embedding; every layer is a parallel block, x += mixer(h) + ff(h) with h = tanh-norm(x); the mixer is,
 by the layer's ``type``,
 
-* "attention": windowed grouped-query attention with (partial) rotary encoding, q and k divided by their
-  root mean square per head after the rotation, capped scores, a sink per head, and values mixed with
+* "attention": windowed grouped-query attention with (partial) rotary encoding, q and k of every head scaled
+  to unit root mean square after the rotation, capped scores, a sink per head, and values mixed with
   those of the first such layer (``attention_general``);
 * "mamba2": the selective state-space mixer (``mamba2``);
 * "parallel": two mixers side by side, left a causal grouped-query attention with biased projections and

@@ -85,14 +85,14 @@ class GeneralAttention(Mixer):
     * ``proj_norm``: q <- w_q * q / sqrt(mean(q^2) + eps) over the WHOLE q projection (all heads at
       once), k likewise, before the rotation;
     * a rotary ``position`` that may cover only the first dimensions of a head;
-    * ``head_norm``: q and k of every head divided by their root mean square (no weights), after the
+    * ``head_norm``: q and k of every head scaled to unit root mean square (no weights), after the
       rotation;
     * ``softcap``: score <- cap * tanh(score / cap) after the scale;
     * ``window``: row i sees keys j with 0 <= i - j < window;
     * ``sink``: a learned number per head whose exponential joins the softmax's denominator (no key, no
       value, not scaled, not capped);
     * ``value_mix``: "source" leaves this layer's values (as projected) in ``ctx.shared[mix_key]`` for later
-      layers of the same step; "mix" replaces v by (1 - lambda) v + lambda v_source before it is cached.
+      layers of the same step; "mix" replaces v by v + lambda (v_source - v) before it is cached.
 
     Projection, norms, rotation, mixing and the cache write are one kernel between the q|k|v product
     (float32 result) and the attention kernel; softmax, cap and sink are float32 inside it."""

@@ -77,7 +77,7 @@ def _pad8(n: int) -> int:
 
 @MIXERS.register("gated_delta_channel")
 class ChannelDecayDeltaMixer(Mixer):
-    """The gated delta rule with one decay per head AND key channel:
+    """The gated delta rule with channel-wise decays (a factor for every key channel of every head):
 
         S <- diag(g) S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q        (g [dk] per head)
 

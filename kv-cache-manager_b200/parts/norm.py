@@ -47,8 +47,8 @@ class OutputRMSNorm(Norm):
 
 @NORMS.register("dyt")
 class DynamicTanh(Norm):
-    """A norm without statistics: out = tanh(alpha * x) * w + b, with one learned number alpha and
-    vectors w, b.  ``pending`` is what the layer before left to be added to the stream first: None,
+    """A norm without statistics: out = b + w * tanh(alpha x); alpha is one learned number, w and b
+    are vectors.  ``pending`` is what the layer before left to be added to the stream first: None,
     one float32 tensor, or a list of (float32 tensor, scale) pairs (a block whose sublayers' outputs
     are summed hands them on unsummed); the sum, the stream and the tanh are float32."""
 

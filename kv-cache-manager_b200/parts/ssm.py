@@ -6,9 +6,9 @@ matrix S [state, vdim], zero at a request's start, carried from token to token,
 with x [vdim] per head, B and C [state] per group of heads (head h uses group h // (heads // groups))
 and dt = softplus(raw + dt_bias) per head (no clamp).  One input product gives
 [z: inner | x: inner | B: groups*state | C: groups*state | raw dt: heads], inner = heads * vdim; x, B
-and C pass a short causal convolution over time per channel (with a bias) and SiLU.  The heads'
+and C go through a causal convolution of a few taps along time, channel by channel (with a bias), and SiLU.  The heads'
 outputs, side by side, are multiplied by SiLU(z) and THEN normalised in ``norm_groups`` equal parts
-(each by its own root mean square) and scaled by a weight over inner; output product.
+(every part by the root mean square of its own elements) and scaled by a weight over inner; output product.
 
 State of a request, one float32 row per call site: S of every head, then the last ``taps - 1`` inputs
 of the convolution.  The recurrence is the engine's matrix-state scan in its linear form

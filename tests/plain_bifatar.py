@@ -152,7 +152,7 @@ def left_mixer(h, W, p, m, eps):
 
 
 def right_mixer(h, W, p, m, eps):
-    """Gated delta rule with one decay per head and key channel."""
+    """Gated delta rule with channel-wise decays."""
     T = h.shape[0]
     Hn, Hk, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q = silu(causal_conv(lin(h, W[p + "q"]), W[p + "q.conv"])).view(T, Hk, dk)

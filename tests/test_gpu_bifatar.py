@@ -122,7 +122,7 @@ def test_portions_down_to_two_tokens(name, dtype, folders, oracle):
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_unequal_requests_together_with_pages_and_slots_used_again(name, dtype, folders, oracle):
     """Up to three live requests in a pool that cannot hold all requests at once and with three state
-    slots: portions of some beside single tokens of others; a request that ends gives its pages and its
+    slots: some requests bring a portion while others bring one token; a request that ends gives its pages and its
     slot to the next one, which must start from zero state."""
     B = BM.CONFIGS[name]["block_size"]
     lens = LENGTHS[name]
