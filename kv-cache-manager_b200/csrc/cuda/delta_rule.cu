@@ -53,6 +53,71 @@ delta_conv_kernel(const T* __restrict__ proj, int ldp, const float* __restrict__
   out[size_t(row) * channels + c] = silu_f(acc);
 }
 
+// The same for up to kConvMaxTaps taps with every input read once: a thread owns one channel for a run of
+// kConvRun consecutive rows and keeps the newest taps-1 inputs in registers (they are fetched as above where a
+// request's rows begin inside the run).  The sum runs in the same order as above: the same bits.
+constexpr int kConvMaxTaps = 8, kConvRun = 16;
+template <typename T>
+__global__ void __launch_bounds__(256)
+delta_conv_run_kernel(const T* __restrict__ proj, int ldp, const float* __restrict__ conv_w, int taps,
+                      const float* __restrict__ state, long long state_stride, long long conv_off,
+                      const int* __restrict__ row_seq, const int* __restrict__ seq_q_start,
+                      const int* __restrict__ seq_state_slot, float* __restrict__ out, int channels, int rows,
+                      const float* __restrict__ bias) {
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  const int r0 = blockIdx.x * kConvRun, r1 = min(rows, r0 + kConvRun);
+  float w[kConvMaxTaps], hist[kConvMaxTaps - 1];
+#pragma unroll
+  for (int j = 0; j < kConvMaxTaps; ++j) w[j] = j < taps ? conv_w[size_t(c) * taps + j] : 0.f;
+#pragma unroll
+  for (int j = 0; j < kConvMaxTaps - 1; ++j) hist[j] = 0.f;
+  const float b = bias ? bias[c] : 0.f;
+  // the run's inputs and requests first, all loads in flight together; then the rows in order from registers
+  float curv[kConvRun];
+  int seqv[kConvRun];
+#pragma unroll
+  for (int i = 0; i < kConvRun; ++i) {
+    const int row = r0 + i;
+    seqv[i] = row < r1 ? row_seq[row] : -1;
+    curv[i] = row < r1 ? ldf(proj + size_t(row) * ldp + c) : 0.f;
+  }
+  float wl = w[0];                                     // the current token's weight is the last tap's
+#pragma unroll
+  for (int j = 1; j < kConvMaxTaps; ++j) wl = (j == taps - 1) ? w[j] : wl;
+  int prev_seq = -1;
+#pragma unroll
+  for (int i = 0; i < kConvRun; ++i) {
+    const int row = r0 + i;
+    if (row >= r1) break;
+    const int s = seqv[i];
+    if (s != prev_seq) {                               // a request's rows begin here (or the run does)
+      prev_seq = s;
+      const int q0 = seq_q_start[s], slot = seq_state_slot[s], local = row - q0;
+      const float* kept = slot >= 0 ? state + slot * state_stride + conv_off : nullptr;
+#pragma unroll
+      for (int j = 0; j < kConvMaxTaps - 1; ++j) {
+        if (j < taps - 1) {
+          const int l = local - (taps - 1 - j);
+          hist[j] = l >= 0 ? ldf(proj + size_t(q0 + l) * ldp + c) : (kept ? kept[size_t(taps - 1 + l) * channels + c] : 0.f);
+        }
+      }
+    }
+    const float cur = curv[i];
+    float acc = b;
+#pragma unroll
+    for (int j = 0; j < kConvMaxTaps - 1; ++j)
+      if (j < taps - 1) acc = fmaf(w[j], hist[j], acc);
+    acc = fmaf(wl, cur, acc);
+    out[size_t(row) * channels + c] = silu_f(acc);
+#pragma unroll
+    for (int j = 0; j < kConvMaxTaps - 2; ++j) hist[j] = hist[j + 1];
+    // the newest input takes the place taps-2 (all places from there on hold it: only j < taps-1 is read)
+#pragma unroll
+    for (int j = 0; j < kConvMaxTaps - 1; ++j) hist[j] = (j >= taps - 2) ? cur : hist[j];
+  }
+}
+
 // After the convolution has read it: the state keeps the last taps-1 inputs of each request.
 // One thread owns one (request, channel) and moves old entries down before it overwrites them.
 template <typename T>
@@ -403,8 +468,13 @@ int launch_delta_conv(const void* proj, int ldp, const float* conv_w, int taps, 
                                                                seq_q_start, seq_state_slot, out, channels, bias);
     return KVCM_LAUNCH_RESULT();
   }
-  delta_conv_kernel<T><<<dim3(rows, by), 256, 0, s>>>((const T*)proj, ldp, conv_w, taps, state, state_stride, conv_off,
-                                                      row_seq, seq_q_start, seq_state_slot, out, channels, bias);
+  if (taps <= kConvMaxTaps)
+    delta_conv_run_kernel<T><<<dim3((rows + kConvRun - 1) / kConvRun, by), 256, 0, s>>>(
+        (const T*)proj, ldp, conv_w, taps, state, state_stride, conv_off, row_seq, seq_q_start, seq_state_slot, out, channels,
+        rows, bias);
+  else
+    delta_conv_kernel<T><<<dim3(rows, by), 256, 0, s>>>((const T*)proj, ldp, conv_w, taps, state, state_stride, conv_off,
+                                                        row_seq, seq_q_start, seq_state_slot, out, channels, bias);
   int rc = KVCM_LAUNCH_RESULT();
   if (rc || taps == 1) return rc;
   delta_conv_state_kernel<T><<<dim3(seqs, by), 256, 0, s>>>((const T*)proj, ldp, taps, state, state_stride, conv_off,
